@@ -1,0 +1,291 @@
+// C ABI of the sm_100a residual LayerNorm path: argument checks, dropout
+// constants, alignment-based kernel selection and launches.  No torch here.
+#include "rln_sm100.h"
+
+#include <cuda_runtime.h>
+
+#include "rln_launch.h"
+
+namespace {
+
+thread_local int tls_last_cuda_error = 0;
+
+int cuda_failed(cudaError_t error) {
+    tls_last_cuda_error = static_cast<int>(error);
+    return RLN_ERR_CUDA;
+}
+
+bool supported_hidden(int32_t hidden) {
+    return hidden == 128 || hidden == 256 || hidden == 384 || hidden == 512
+        || hidden == 768 || hidden == 1024;
+}
+
+bool aligned_to(const void* pointer, uintptr_t bytes) {
+    return (reinterpret_cast<uintptr_t>(pointer) & (bytes - 1)) == 0;
+}
+
+// SM count of the current device, cached per device ordinal.
+int current_sm_count(int* out) {
+    static int cached[64] = {0};
+    int device = 0;
+    cudaError_t error = cudaGetDevice(&device);
+    if (error != cudaSuccess) {
+        return cuda_failed(error);
+    }
+    if (device >= 0 && device < 64 && cached[device] > 0) {
+        *out = cached[device];
+        return RLN_OK;
+    }
+    int count = 0;
+    error = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    if (error != cudaSuccess) {
+        return cuda_failed(error);
+    }
+    if (device >= 0 && device < 64) {
+        cached[device] = count;
+    }
+    *out = count;
+    return RLN_OK;
+}
+
+// threshold and scale exactly as the reference computes them
+// (csrc/residual_layer_norm_kernel.hip:896-899): p is narrowed to fp32 first.
+uint32_t dropout_threshold(float dropout_p) {
+    return static_cast<uint32_t>(static_cast<double>(dropout_p) * 4294967296.0);
+}
+
+float dropout_scale(float dropout_p, bool active) {
+    return active ? 1.0f / (1.0f - dropout_p) : 1.0f;
+}
+
+}  // namespace
+
+extern "C" int rln_sm100_abi_version(void) { return RLN_SM100_ABI_VERSION; }
+
+extern "C" const char* rln_sm100_status_string(int status) {
+    switch (status) {
+        case RLN_OK: return "ok";
+        case RLN_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case RLN_ERR_HIDDEN_SIZE: return "unsupported native hidden size";
+        case RLN_ERR_ROW_COUNT: return "empty tensors are unsupported";
+        case RLN_ERR_DROPOUT_P: return "dropout_p must be in [0, 1)";
+        case RLN_ERR_EPS: return "eps must be positive";
+        case RLN_ERR_ALIGNMENT: return "a pointer is not aligned to its element size";
+        case RLN_ERR_WORKSPACE: return "workspace is missing or too small";
+        case RLN_ERR_CUDA: return "a CUDA runtime call failed";
+        case RLN_ERR_HOST_BUFFERS: return "invalid host-buffer pipeline arguments";
+        case RLN_ERR_LIMIT: return "size exceeds a fixed maximum of this entry point";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int rln_sm100_last_cuda_error(void) { return tls_last_cuda_error; }
+
+extern "C" int rln_sm100_forward(
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    float* updated,
+    float* normalized,
+    float* mean,
+    float* rstd,
+    uint32_t* dropout_mask,
+    int64_t rows,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    uint64_t seed,
+    uint64_t offset,
+    int64_t row_base,
+    void* stream) {
+    if (!supported_hidden(hidden)) {
+        return RLN_ERR_HIDDEN_SIZE;
+    }
+    if (rows <= 0) {
+        return RLN_ERR_ROW_COUNT;
+    }
+    if (!(dropout_p >= 0.0f && dropout_p < 1.0f)) {
+        return RLN_ERR_DROPOUT_P;
+    }
+    if (!(eps > 0.0f)) {
+        return RLN_ERR_EPS;
+    }
+    if (x == nullptr || branch == nullptr || weight == nullptr || bias == nullptr
+        || updated == nullptr || normalized == nullptr || mean == nullptr || rstd == nullptr
+        || (dropout_active && dropout_mask == nullptr)) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    const uintptr_t branch_element = branch_is_half ? 2 : 4;
+    if (!aligned_to(x, 4) || !aligned_to(branch, branch_element) || !aligned_to(weight, 4)
+        || !aligned_to(bias, 4) || !aligned_to(updated, 4) || !aligned_to(normalized, 4)
+        || !aligned_to(mean, 4) || !aligned_to(rstd, 4)
+        || (dropout_active && !aligned_to(dropout_mask, 4))) {
+        return RLN_ERR_ALIGNMENT;
+    }
+    const bool vector_ok = aligned_to(x, 16) && aligned_to(branch, branch_element * 4)
+        && aligned_to(weight, 16) && aligned_to(bias, 16) && aligned_to(updated, 16)
+        && aligned_to(normalized, 16);
+
+    rln::ForwardParams params;
+    params.x = x;
+    params.branch = branch;
+    params.weight = weight;
+    params.bias = bias;
+    params.updated = updated;
+    params.normalized = normalized;
+    params.mean = mean;
+    params.rstd = rstd;
+    params.mask = dropout_mask;
+    params.rows = rows;
+    params.row_base = row_base;
+    params.scale = dropout_scale(dropout_p, dropout_active != 0);
+    params.eps = eps;
+    params.threshold = dropout_threshold(dropout_p);
+    params.seed_lo = static_cast<uint32_t>(seed);
+    params.seed_hi = static_cast<uint32_t>(seed >> 32);
+    params.offset_lo = static_cast<uint32_t>(offset);
+    params.offset_hi = static_cast<uint32_t>(offset >> 32);
+
+    const cudaError_t error = rln::launch_forward(
+        hidden,
+        branch_is_half != 0,
+        dropout_active != 0,
+        vector_ok,
+        params,
+        static_cast<cudaStream_t>(stream));
+    return error == cudaSuccess ? RLN_OK : cuda_failed(error);
+}
+
+extern "C" int64_t rln_sm100_backward_workspace_bytes(
+    int64_t rows,
+    int32_t hidden,
+    int32_t deterministic) {
+    if (!supported_hidden(hidden)) {
+        return RLN_ERR_HIDDEN_SIZE;
+    }
+    if (rows <= 0) {
+        return RLN_ERR_ROW_COUNT;
+    }
+    if (!deterministic) {
+        return 0;
+    }
+    int sm_count = 0;
+    const int status = current_sm_count(&sm_count);
+    if (status != RLN_OK) {
+        return status;
+    }
+    const int grid = rln::backward_grid(hidden, rows, sm_count);
+    return static_cast<int64_t>(grid) * 2 * hidden * static_cast<int64_t>(sizeof(float));
+}
+
+extern "C" int rln_sm100_backward(
+    const float* grad_updated,
+    const float* grad_normalized,
+    const float* updated,
+    const float* weight,
+    const float* mean,
+    const float* rstd,
+    const uint32_t* dropout_mask,
+    float* grad_x,
+    void* grad_branch,
+    float* grad_parameters,
+    void* workspace,
+    int64_t workspace_bytes,
+    int64_t rows,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int32_t dropout_active,
+    float dropout_p,
+    int32_t deterministic,
+    void* stream_pointer) {
+    if (!supported_hidden(hidden)) {
+        return RLN_ERR_HIDDEN_SIZE;
+    }
+    if (rows <= 0) {
+        return RLN_ERR_ROW_COUNT;
+    }
+    if (!(dropout_p >= 0.0f && dropout_p < 1.0f)) {
+        return RLN_ERR_DROPOUT_P;
+    }
+    if (grad_updated == nullptr || grad_normalized == nullptr || updated == nullptr
+        || weight == nullptr || mean == nullptr || rstd == nullptr || grad_x == nullptr
+        || grad_branch == nullptr || (dropout_active && dropout_mask == nullptr)) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    const uintptr_t branch_element = branch_is_half ? 2 : 4;
+    if (!aligned_to(grad_updated, 4) || !aligned_to(grad_normalized, 4) || !aligned_to(updated, 4)
+        || !aligned_to(weight, 4) || !aligned_to(mean, 4) || !aligned_to(rstd, 4)
+        || !aligned_to(grad_x, 4) || !aligned_to(grad_branch, branch_element)
+        || (dropout_active && !aligned_to(dropout_mask, 4))
+        || (grad_parameters != nullptr && !aligned_to(grad_parameters, 4))) {
+        return RLN_ERR_ALIGNMENT;
+    }
+    const bool parameters = grad_parameters != nullptr;
+    const bool vector_ok = aligned_to(grad_updated, 16) && aligned_to(grad_normalized, 16)
+        && aligned_to(updated, 16) && aligned_to(weight, 16) && aligned_to(grad_x, 16)
+        && aligned_to(grad_branch, branch_element * 4)
+        && (!parameters || aligned_to(grad_parameters, 16));
+
+    int sm_count = 0;
+    const int status = current_sm_count(&sm_count);
+    if (status != RLN_OK) {
+        return status;
+    }
+    const int grid = rln::backward_grid(hidden, rows, sm_count);
+    const bool two_pass = parameters && deterministic != 0;
+    if (two_pass) {
+        const int64_t needed =
+            static_cast<int64_t>(grid) * 2 * hidden * static_cast<int64_t>(sizeof(float));
+        if (workspace == nullptr || workspace_bytes < needed || !aligned_to(workspace, 16)) {
+            return RLN_ERR_WORKSPACE;
+        }
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_pointer);
+
+    rln::BackwardParams params;
+    params.grad_updated = grad_updated;
+    params.grad_normalized = grad_normalized;
+    params.updated = updated;
+    params.weight = weight;
+    params.mean = mean;
+    params.rstd = rstd;
+    params.mask = dropout_mask;
+    params.grad_x = grad_x;
+    params.grad_branch = grad_branch;
+    params.grad_parameters = grad_parameters;
+    params.partials = static_cast<float*>(workspace);
+    params.rows = rows;
+    params.scale = dropout_scale(dropout_p, dropout_active != 0);
+    params.deterministic = two_pass ? 1 : 0;
+
+    if (parameters && !two_pass) {
+        const cudaError_t error = cudaMemsetAsync(
+            grad_parameters, 0, static_cast<size_t>(2) * hidden * sizeof(float), stream);
+        if (error != cudaSuccess) {
+            return cuda_failed(error);
+        }
+    }
+    cudaError_t error = rln::launch_backward(
+        hidden,
+        branch_is_half != 0,
+        dropout_active != 0,
+        parameters,
+        vector_ok,
+        params,
+        grid,
+        stream);
+    if (error != cudaSuccess) {
+        return cuda_failed(error);
+    }
+    if (two_pass) {
+        error = rln::launch_reduce_partials(
+            static_cast<const float*>(workspace), grad_parameters, grid, 2 * hidden, stream);
+        if (error != cudaSuccess) {
+            return cuda_failed(error);
+        }
+    }
+    return RLN_OK;
+}

@@ -1,0 +1,108 @@
+// Backward kernel instantiations, the persistent-grid rule and the dispatch ladder.
+#include "rln_launch.h"
+
+namespace rln {
+namespace {
+
+template <int H>
+int backward_grid_hidden(int64_t rows, int sm_count) {
+    constexpr int64_t kRowsPerCta =
+        static_cast<int64_t>(BackwardTune<H>::kWarps) * BackwardTune<H>::kRows;
+    const int64_t needed = (rows + kRowsPerCta - 1) / kRowsPerCta;
+    const int64_t resident = static_cast<int64_t>(sm_count) * BackwardTune<H>::kCtasPerSm;
+    return static_cast<int>(needed < resident ? needed : resident);
+}
+
+template <int H, typename BranchT, bool kDropout, bool kParams, bool kAligned>
+cudaError_t launch_backward_typed(const BackwardParams& params, int grid, cudaStream_t stream) {
+    constexpr int kWarps = BackwardTune<H>::kWarps;
+    constexpr int kRows = BackwardTune<H>::kRows;
+    rln_backward_kernel<H, BranchT, kDropout, kParams, kAligned, kWarps, kRows>
+        <<<static_cast<unsigned>(grid), kWarps * kWarpSize, 0, stream>>>(params);
+    return cudaGetLastError();
+}
+
+template <int H, bool kAligned>
+cudaError_t launch_backward_hidden(
+    bool branch_is_half,
+    bool dropout,
+    bool parameters,
+    const BackwardParams& params,
+    int grid,
+    cudaStream_t stream) {
+#define RLN_BWD_CASE(HALF, DROP, PARAMS)                                                        \
+    if (branch_is_half == HALF && dropout == DROP && parameters == PARAMS) {                    \
+        if constexpr (HALF) {                                                                   \
+            return launch_backward_typed<H, __half, DROP, PARAMS, kAligned>(params, grid, stream); \
+        } else {                                                                                \
+            return launch_backward_typed<H, float, DROP, PARAMS, kAligned>(params, grid, stream);  \
+        }                                                                                       \
+    }
+    RLN_BWD_CASE(true, true, true)
+    RLN_BWD_CASE(true, true, false)
+    RLN_BWD_CASE(true, false, true)
+    RLN_BWD_CASE(true, false, false)
+    RLN_BWD_CASE(false, true, true)
+    RLN_BWD_CASE(false, true, false)
+    RLN_BWD_CASE(false, false, true)
+    RLN_BWD_CASE(false, false, false)
+#undef RLN_BWD_CASE
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+int backward_grid(int hidden, int64_t rows, int sm_count) {
+    switch (hidden) {
+        case 128: return backward_grid_hidden<128>(rows, sm_count);
+        case 256: return backward_grid_hidden<256>(rows, sm_count);
+        case 384: return backward_grid_hidden<384>(rows, sm_count);
+        case 512: return backward_grid_hidden<512>(rows, sm_count);
+        case 768: return backward_grid_hidden<768>(rows, sm_count);
+        case 1024: return backward_grid_hidden<1024>(rows, sm_count);
+        default: return 0;
+    }
+}
+
+cudaError_t launch_backward(
+    int hidden,
+    bool branch_is_half,
+    bool dropout,
+    bool parameters,
+    bool aligned,
+    const BackwardParams& params,
+    int grid,
+    cudaStream_t stream) {
+#define RLN_BWD_HIDDEN(HIDDEN)                                                               \
+    case HIDDEN:                                                                             \
+        return aligned                                                                       \
+            ? launch_backward_hidden<HIDDEN, true>(                                          \
+                  branch_is_half, dropout, parameters, params, grid, stream)                 \
+            : launch_backward_hidden<HIDDEN, false>(                                         \
+                  branch_is_half, dropout, parameters, params, grid, stream);
+    switch (hidden) {
+        RLN_BWD_HIDDEN(128)
+        RLN_BWD_HIDDEN(256)
+        RLN_BWD_HIDDEN(384)
+        RLN_BWD_HIDDEN(512)
+        RLN_BWD_HIDDEN(768)
+        RLN_BWD_HIDDEN(1024)
+        default: return cudaErrorInvalidValue;
+    }
+#undef RLN_BWD_HIDDEN
+}
+
+cudaError_t launch_reduce_partials(
+    const float* partials,
+    float* out,
+    int partial_count,
+    int columns,
+    cudaStream_t stream) {
+    constexpr int kSegments = 8;
+    const int blocks = (columns + kWarpSize - 1) / kWarpSize;
+    rln_reduce_partials_kernel<kSegments>
+        <<<blocks, kSegments * kWarpSize, 0, stream>>>(partials, out, partial_count, columns);
+    return cudaGetLastError();
+}
+
+}  // namespace rln

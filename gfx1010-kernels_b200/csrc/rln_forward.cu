@@ -1,0 +1,68 @@
+// Forward kernel instantiations and their dispatch ladder.
+#include "rln_launch.h"
+
+namespace rln {
+namespace {
+
+template <int H, typename BranchT, bool kDropout, bool kAligned>
+cudaError_t launch_forward_typed(const ForwardParams& params, cudaStream_t stream) {
+    constexpr int kWarps = ForwardTune<H>::kWarps;
+    constexpr int kRows = ForwardTune<H>::kRows;
+    constexpr int64_t kRowsPerCta = static_cast<int64_t>(kWarps) * kRows;
+    int64_t blocks = (params.rows + kRowsPerCta - 1) / kRowsPerCta;
+    if (blocks > 0x7fffffff) {
+        blocks = 0x7fffffff;  // the kernel grid-strides over the remainder
+    }
+    rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows>
+        <<<static_cast<unsigned>(blocks), kWarps * kWarpSize, 0, stream>>>(params);
+    return cudaGetLastError();
+}
+
+template <int H>
+cudaError_t launch_forward_hidden(
+    bool branch_is_half,
+    bool dropout,
+    bool aligned,
+    const ForwardParams& params,
+    cudaStream_t stream) {
+#define RLN_FWD_CASE(HALF, DROP, ALIGNED)                                                   \
+    if (branch_is_half == HALF && dropout == DROP && aligned == ALIGNED) {                  \
+        if constexpr (HALF) {                                                               \
+            return launch_forward_typed<H, __half, DROP, ALIGNED>(params, stream);          \
+        } else {                                                                            \
+            return launch_forward_typed<H, float, DROP, ALIGNED>(params, stream);           \
+        }                                                                                   \
+    }
+    RLN_FWD_CASE(true, true, true)
+    RLN_FWD_CASE(true, false, true)
+    RLN_FWD_CASE(false, true, true)
+    RLN_FWD_CASE(false, false, true)
+    RLN_FWD_CASE(true, true, false)
+    RLN_FWD_CASE(true, false, false)
+    RLN_FWD_CASE(false, true, false)
+    RLN_FWD_CASE(false, false, false)
+#undef RLN_FWD_CASE
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t launch_forward(
+    int hidden,
+    bool branch_is_half,
+    bool dropout,
+    bool aligned,
+    const ForwardParams& params,
+    cudaStream_t stream) {
+    switch (hidden) {
+        case 128: return launch_forward_hidden<128>(branch_is_half, dropout, aligned, params, stream);
+        case 256: return launch_forward_hidden<256>(branch_is_half, dropout, aligned, params, stream);
+        case 384: return launch_forward_hidden<384>(branch_is_half, dropout, aligned, params, stream);
+        case 512: return launch_forward_hidden<512>(branch_is_half, dropout, aligned, params, stream);
+        case 768: return launch_forward_hidden<768>(branch_is_half, dropout, aligned, params, stream);
+        case 1024: return launch_forward_hidden<1024>(branch_is_half, dropout, aligned, params, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace rln

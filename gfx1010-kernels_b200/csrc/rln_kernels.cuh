@@ -1,0 +1,636 @@
+// Device code of the sm_100a fused residual-add + dropout + LayerNorm path.
+//
+// Design (B200, 148 SMs, HBM3e): the operator has no contraction and does
+// O(10) flops per element, so every kernel here is an HBM streaming kernel.
+//   * One warp owns one row at a time.  All supported widths are multiples of
+//     128, so lane l owns the float4 chunks l, l+32, l+64, ... of the row and
+//     every global access of a warp is one fully coalesced 512-byte (fp32) or
+//     256-byte (fp16 branch) transaction.  The whole row stays in registers
+//     between the load and the store: row data is read from HBM exactly once.
+//   * Row mean and the centred variance are two 5-step xor-shuffle butterflies;
+//     there is no __syncthreads anywhere in the row loop.
+//   * The dropout keep decision of the four columns of a chunk is one
+//     Philox4x32-10 call keyed on (seed, offset, global element-group index);
+//     eight neighbouring lanes OR their nibbles into one 32-bit mask word.
+//   * The backward reads grad_updated, grad_normalized and updated once,
+//     writes grad_x and grad_branch, and accumulates the grad_weight/grad_bias
+//     partial sums of the rows a warp visits in registers (persistent grid).
+//     The warps of a CTA combine in shared memory in warp order; the CTA then
+//     either issues vector fp32 atomics or stores its partial for the
+//     fixed-order second pass.
+//
+// The arithmetic follows the reference project's HIP kernels
+// (csrc/residual_layer_norm_kernel.hip): forward :483-545, backward-input
+// :572-617, parameter sums :741-760; the launch geometry, the Philox counter
+// layout and the single-pass backward do not.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rln {
+
+constexpr int kWarpSize = 32;
+constexpr unsigned kFullMask = 0xffffffffu;
+
+struct ForwardParams {
+    const float* x;
+    const void* branch;
+    const float* weight;
+    const float* bias;
+    float* updated;
+    float* normalized;
+    float* mean;
+    float* rstd;
+    uint32_t* mask;
+    int64_t rows;
+    int64_t row_base;
+    float scale;
+    float eps;
+    uint32_t threshold;
+    uint32_t seed_lo;
+    uint32_t seed_hi;
+    uint32_t offset_lo;
+    uint32_t offset_hi;
+};
+
+struct BackwardParams {
+    const float* grad_updated;
+    const float* grad_normalized;
+    const float* updated;
+    const float* weight;
+    const float* mean;
+    const float* rstd;
+    const uint32_t* mask;
+    float* grad_x;
+    void* grad_branch;
+    float* grad_parameters;  // [2, H]; atomics target (fast path)
+    float* partials;         // [gridDim.x, 2, H]; deterministic path
+    int64_t rows;
+    float scale;
+    int deterministic;
+};
+
+// ---------------------------------------------------------------------------
+// Philox4x32-10 (Salmon et al., SC'11), written out; one call = 4 random words.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint4 counter, uint32_t key0, uint32_t key1) {
+    constexpr uint32_t kM0 = 0xD2511F53u;
+    constexpr uint32_t kM1 = 0xCD9E8D57u;
+    constexpr uint32_t kW0 = 0x9E3779B9u;
+    constexpr uint32_t kW1 = 0xBB67AE85u;
+#pragma unroll
+    for (int round = 0; round < 10; ++round) {
+        const uint32_t hi0 = __umulhi(kM0, counter.x);
+        const uint32_t lo0 = kM0 * counter.x;
+        const uint32_t hi1 = __umulhi(kM1, counter.z);
+        const uint32_t lo1 = kM1 * counter.z;
+        counter = make_uint4(hi1 ^ counter.y ^ key0, lo1, hi0 ^ counter.w ^ key1, lo0);
+        key0 += kW0;
+        key1 += kW1;
+    }
+    return counter;
+}
+
+// ---------------------------------------------------------------------------
+// Global-memory access.  Row data is touched once, so it is streamed
+// (evict-first); kAligned == false is the 4-byte-aligned fallback with the
+// same lane->column mapping and therefore bit-identical arithmetic.
+// ---------------------------------------------------------------------------
+// Cache policy of the streamed accesses (compile-time tunables).
+//   RLN_LOAD_POLICY : 0 plain, 1 ld.global.nc (__ldg), 2 evict-first (__ldcs),
+//                     3 ld.global.nc.L1::no_allocate
+//   RLN_STORE_POLICY: 0 plain, 1 evict-first (__stcs), 2 write-through (__stwt)
+#ifndef RLN_LOAD_POLICY
+#define RLN_LOAD_POLICY 2
+#endif
+#ifndef RLN_STORE_POLICY
+#define RLN_STORE_POLICY 1
+#endif
+
+__device__ __forceinline__ float4 stream_load(const float4* p) {
+#if RLN_LOAD_POLICY == 0
+    return *p;
+#elif RLN_LOAD_POLICY == 1
+    return __ldg(p);
+#elif RLN_LOAD_POLICY == 2
+    return __ldcs(p);
+#else
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+#endif
+}
+__device__ __forceinline__ uint2 stream_load(const uint2* p) {
+#if RLN_LOAD_POLICY == 0
+    return *p;
+#elif RLN_LOAD_POLICY == 1
+    return __ldg(p);
+#elif RLN_LOAD_POLICY == 2
+    return __ldcs(p);
+#else
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];"
+                 : "=r"(v.x), "=r"(v.y)
+                 : "l"(p));
+    return v;
+#endif
+}
+__device__ __forceinline__ void stream_store(float4* p, float4 v) {
+#if RLN_STORE_POLICY == 0
+    *p = v;
+#elif RLN_STORE_POLICY == 1
+    __stcs(p, v);
+#else
+    __stwt(p, v);
+#endif
+}
+__device__ __forceinline__ void stream_store(uint2* p, uint2 v) {
+#if RLN_STORE_POLICY == 0
+    *p = v;
+#elif RLN_STORE_POLICY == 1
+    __stcs(p, v);
+#else
+    __stwt(p, v);
+#endif
+}
+
+template <bool kAligned>
+__device__ __forceinline__ float4 load_f4(const float* base, int64_t chunk) {
+    if constexpr (kAligned) {
+        return stream_load(reinterpret_cast<const float4*>(base) + chunk);
+    } else {
+        const float* p = base + chunk * 4;
+        return make_float4(p[0], p[1], p[2], p[3]);
+    }
+}
+
+template <bool kAligned>
+__device__ __forceinline__ void store_f4(float* base, int64_t chunk, float4 v) {
+    if constexpr (kAligned) {
+        stream_store(reinterpret_cast<float4*>(base) + chunk, v);
+    } else {
+        float* p = base + chunk * 4;
+        p[0] = v.x;
+        p[1] = v.y;
+        p[2] = v.z;
+        p[3] = v.w;
+    }
+}
+
+// Small, reused vectors (weight, bias): default caching so they stay in L1.
+__device__ __forceinline__ float4 load_param4(const float* base, int chunk) {
+    // weight/bias come from the caching allocator or cudaMalloc: 16-byte
+    // alignment is checked on the host, scalar fallback otherwise.
+    return __ldg(reinterpret_cast<const float4*>(base) + chunk);
+}
+__device__ __forceinline__ float4 load_param4_scalar(const float* base, int chunk) {
+    const float* p = base + chunk * 4;
+    return make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
+}
+template <bool kAligned>
+__device__ __forceinline__ float4 load_param(const float* base, int chunk) {
+    if constexpr (kAligned) {
+        return load_param4(base, chunk);
+    } else {
+        return load_param4_scalar(base, chunk);
+    }
+}
+
+// Branch-typed access: four consecutive elements of the branch tensor.
+template <typename T>
+struct BranchIO;
+
+template <>
+struct BranchIO<float> {
+    template <bool kAligned>
+    static __device__ __forceinline__ float4 load(const void* base, int64_t chunk) {
+        return load_f4<kAligned>(static_cast<const float*>(base), chunk);
+    }
+    template <bool kAligned>
+    static __device__ __forceinline__ void store(void* base, int64_t chunk, float4 v) {
+        store_f4<kAligned>(static_cast<float*>(base), chunk, v);
+    }
+    static __device__ __forceinline__ float round(float v) { return v; }
+};
+
+template <>
+struct BranchIO<__half> {
+    template <bool kAligned>
+    static __device__ __forceinline__ float4 load(const void* base, int64_t chunk) {
+        if constexpr (kAligned) {
+            const uint2 raw = stream_load(static_cast<const uint2*>(base) + chunk);
+            const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+            const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            return make_float4(lo.x, lo.y, hi.x, hi.y);
+        } else {
+            const __half* p = static_cast<const __half*>(base) + chunk * 4;
+            return make_float4(
+                __half2float(p[0]), __half2float(p[1]), __half2float(p[2]), __half2float(p[3]));
+        }
+    }
+    template <bool kAligned>
+    static __device__ __forceinline__ void store(void* base, int64_t chunk, float4 v) {
+        if constexpr (kAligned) {
+            const __half2 lo = __floats2half2_rn(v.x, v.y);
+            const __half2 hi = __floats2half2_rn(v.z, v.w);
+            uint2 raw;
+            raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+            raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+            stream_store(static_cast<uint2*>(base) + chunk, raw);
+        } else {
+            __half* p = static_cast<__half*>(base) + chunk * 4;
+            p[0] = __float2half_rn(v.x);
+            p[1] = __float2half_rn(v.y);
+            p[2] = __float2half_rn(v.z);
+            p[3] = __float2half_rn(v.w);
+        }
+    }
+    static __device__ __forceinline__ float round(float v) {
+        return __half2float(__float2half_rn(v));
+    }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int delta = 16; delta > 0; delta >>= 1) {
+        v += __shfl_xor_sync(kFullMask, v, delta);
+    }
+    return v;
+}
+
+// dropped = round_to_branch(float(b) * keep * scale): two separate fp32
+// multiplies (no contraction) so the result is bit-identical to the torch
+// decomposition evaluated with the same mask.
+template <typename BranchT>
+__device__ __forceinline__ float drop_one(float b, bool keep, float scale) {
+    return BranchIO<BranchT>::round(__fmul_rn(__fmul_rn(b, keep ? 1.0f : 0.0f), scale));
+}
+
+// ---------------------------------------------------------------------------
+// Forward.  grid-stride over groups of kRows consecutive rows per warp.
+// ---------------------------------------------------------------------------
+template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kRows,
+          int kMinCtas = 1>
+__global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
+rln_forward_kernel(const ForwardParams p) {
+    static_assert(H % 128 == 0, "hidden must be a multiple of 128");
+    constexpr int V = H / 128;          // float4 chunks per lane
+    constexpr int kChunksPerRow = H / 4;
+    constexpr int kWordsPerRow = H / 32;
+    constexpr float kInvH = 1.0f / static_cast<float>(H);
+    using IO = BranchIO<BranchT>;
+
+    const int lane = threadIdx.x & (kWarpSize - 1);
+    const int warp = threadIdx.x / kWarpSize;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRows;
+
+    for (int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRows;
+         first < p.rows; first += stride) {
+        float4 u[kRows][V];
+        float4 b[kRows][V];
+        uint32_t nibble[kRows][V];
+
+        // 1. issue every load of this warp's rows
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int64_t row = first + r;
+            if (row < p.rows) {
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
+                    u[r][k] = load_f4<kAligned>(p.x, chunk);
+                    b[r][k] = IO::template load<kAligned>(p.branch, chunk);
+                }
+            }
+        }
+
+        // 2. keep decisions (independent of the loads: overlaps their latency)
+        if constexpr (kDropout) {
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                const int64_t row = first + r;
+                if (row < p.rows) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        const uint64_t group =
+                            static_cast<uint64_t>(p.row_base + row) * kChunksPerRow
+                            + static_cast<uint64_t>(lane + k * kWarpSize);
+                        const uint4 random = philox4x32_10(
+                            make_uint4(
+                                p.offset_lo,
+                                p.offset_hi,
+                                static_cast<uint32_t>(group),
+                                static_cast<uint32_t>(group >> 32)),
+                            p.seed_lo,
+                            p.seed_hi);
+                        nibble[r][k] =
+                            (random.x >= p.threshold ? 1u : 0u)
+                            | (random.y >= p.threshold ? 2u : 0u)
+                            | (random.z >= p.threshold ? 4u : 0u)
+                            | (random.w >= p.threshold ? 8u : 0u);
+                    }
+                }
+            }
+        }
+
+        // 3. per row: residual add, statistics, affine, stores
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int64_t row = first + r;
+            if (row >= p.rows) {
+                continue;  // warp-uniform
+            }
+            float sum = 0.0f;
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                float4 dropped = b[r][k];
+                if constexpr (kDropout) {
+                    const uint32_t n = nibble[r][k];
+                    dropped.x = drop_one<BranchT>(dropped.x, n & 1u, p.scale);
+                    dropped.y = drop_one<BranchT>(dropped.y, n & 2u, p.scale);
+                    dropped.z = drop_one<BranchT>(dropped.z, n & 4u, p.scale);
+                    dropped.w = drop_one<BranchT>(dropped.w, n & 8u, p.scale);
+                }
+                float4 value = u[r][k];
+                value.x = __fadd_rn(value.x, dropped.x);
+                value.y = __fadd_rn(value.y, dropped.y);
+                value.z = __fadd_rn(value.z, dropped.z);
+                value.w = __fadd_rn(value.w, dropped.w);
+                u[r][k] = value;
+                const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
+                store_f4<kAligned>(p.updated, chunk, value);
+                sum += (value.x + value.y) + (value.z + value.w);
+            }
+            const float row_mean = warp_sum(sum) * kInvH;
+            float square_sum = 0.0f;
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                const float cx = u[r][k].x - row_mean;
+                const float cy = u[r][k].y - row_mean;
+                const float cz = u[r][k].z - row_mean;
+                const float cw = u[r][k].w - row_mean;
+                square_sum += (cx * cx + cy * cy) + (cz * cz + cw * cw);
+            }
+            const float variance = warp_sum(square_sum) * kInvH;
+            const float row_rstd = rsqrtf(variance + p.eps);
+            if (lane == 0) {
+                p.mean[row] = row_mean;
+                p.rstd[row] = row_rstd;
+            }
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                const int pchunk = lane + k * kWarpSize;
+                const float4 gamma = load_param<kAligned>(p.weight, pchunk);
+                const float4 beta = load_param<kAligned>(p.bias, pchunk);
+                float4 out;
+                out.x = (u[r][k].x - row_mean) * row_rstd * gamma.x + beta.x;
+                out.y = (u[r][k].y - row_mean) * row_rstd * gamma.y + beta.y;
+                out.z = (u[r][k].z - row_mean) * row_rstd * gamma.z + beta.z;
+                out.w = (u[r][k].w - row_mean) * row_rstd * gamma.w + beta.w;
+                store_f4<kAligned>(p.normalized, row * kChunksPerRow + pchunk, out);
+            }
+            if constexpr (kDropout) {
+                // chunk c = lane + 32k covers columns 4c..4c+3 -> nibble
+                // (lane & 7) of mask word 4k + lane/8.
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    uint32_t word = nibble[r][k] << (4 * (lane & 7));
+                    word |= __shfl_xor_sync(kFullMask, word, 1);
+                    word |= __shfl_xor_sync(kFullMask, word, 2);
+                    word |= __shfl_xor_sync(kFullMask, word, 4);
+                    if ((lane & 7) == 0) {
+                        p.mask[row * kWordsPerRow + 4 * k + (lane >> 3)] = word;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Backward.  Persistent grid; each warp walks groups of kRows consecutive rows
+// with a fixed stride, so the set and order of rows a warp (and a CTA) sums is
+// a pure function of (rows, gridDim) -- the basis of the bitwise-replay mode.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void red_add_f4(float* address, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :
+                 : "l"(address), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
+template <int H, typename BranchT, bool kDropout, bool kParams, bool kAligned, int kWarps, int kRows,
+          int kMinCtas = 1>
+__global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
+rln_backward_kernel(const BackwardParams p) {
+    static_assert(H % 128 == 0, "hidden must be a multiple of 128");
+    constexpr int V = H / 128;
+    constexpr int kChunksPerRow = H / 4;
+    constexpr int kWordsPerRow = H / 32;
+    constexpr float kInvH = 1.0f / static_cast<float>(H);
+    using IO = BranchIO<BranchT>;
+
+    const int lane = threadIdx.x & (kWarpSize - 1);
+    const int warp = threadIdx.x / kWarpSize;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRows;
+
+    float4 acc_weight[kParams ? V : 1];
+    float4 acc_bias[kParams ? V : 1];
+    if constexpr (kParams) {
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            acc_weight[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            acc_bias[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    }
+
+    for (int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRows;
+         first < p.rows; first += stride) {
+        float4 gy[kRows][V];
+        float4 uu[kRows][V];
+        float4 gu[kRows][V];
+        uint32_t words[kRows][V];
+        float row_mean[kRows];
+        float row_rstd[kRows];
+
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int64_t row = first + r;
+            if (row < p.rows) {
+                row_mean[r] = __ldg(p.mean + row);
+                row_rstd[r] = __ldg(p.rstd + row);
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
+                    gy[r][k] = load_f4<kAligned>(p.grad_normalized, chunk);
+                    uu[r][k] = load_f4<kAligned>(p.updated, chunk);
+                    gu[r][k] = load_f4<kAligned>(p.grad_updated, chunk);
+                    if constexpr (kDropout) {
+                        words[r][k] = __ldg(p.mask + row * kWordsPerRow + 4 * k + (lane >> 3));
+                    }
+                }
+            }
+        }
+
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int64_t row = first + r;
+            if (row >= p.rows) {
+                continue;  // warp-uniform
+            }
+            const float mu = row_mean[r];
+            const float rs = row_rstd[r];
+            float sum_q = 0.0f;
+            float sum_qx = 0.0f;
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                const float4 gamma = load_param<kAligned>(p.weight, lane + k * kWarpSize);
+                float4 xhat;
+                xhat.x = (uu[r][k].x - mu) * rs;
+                xhat.y = (uu[r][k].y - mu) * rs;
+                xhat.z = (uu[r][k].z - mu) * rs;
+                xhat.w = (uu[r][k].w - mu) * rs;
+                const float4 g = gy[r][k];
+                if constexpr (kParams) {
+                    acc_weight[k].x += g.x * xhat.x;
+                    acc_weight[k].y += g.y * xhat.y;
+                    acc_weight[k].z += g.z * xhat.z;
+                    acc_weight[k].w += g.w * xhat.w;
+                    acc_bias[k].x += g.x;
+                    acc_bias[k].y += g.y;
+                    acc_bias[k].z += g.z;
+                    acc_bias[k].w += g.w;
+                }
+                float4 q;
+                q.x = g.x * gamma.x;
+                q.y = g.y * gamma.y;
+                q.z = g.z * gamma.z;
+                q.w = g.w * gamma.w;
+                sum_q += (q.x + q.y) + (q.z + q.w);
+                sum_qx += (q.x * xhat.x + q.y * xhat.y) + (q.z * xhat.z + q.w * xhat.w);
+                gy[r][k] = q;      // reuse registers: weighted gradient
+                uu[r][k] = xhat;   // reuse registers: normalised value
+            }
+#pragma unroll
+            for (int delta = 16; delta > 0; delta >>= 1) {
+                sum_q += __shfl_xor_sync(kFullMask, sum_q, delta);
+                sum_qx += __shfl_xor_sync(kFullMask, sum_qx, delta);
+            }
+            const float mean_q = sum_q * kInvH;
+            const float mean_qx = sum_qx * kInvH;
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
+                float4 total;
+                total.x = gu[r][k].x + rs * (gy[r][k].x - mean_q - uu[r][k].x * mean_qx);
+                total.y = gu[r][k].y + rs * (gy[r][k].y - mean_q - uu[r][k].y * mean_qx);
+                total.z = gu[r][k].z + rs * (gy[r][k].z - mean_q - uu[r][k].z * mean_qx);
+                total.w = gu[r][k].w + rs * (gy[r][k].w - mean_q - uu[r][k].w * mean_qx);
+                store_f4<kAligned>(p.grad_x, chunk, total);
+                if constexpr (kDropout) {
+                    const uint32_t n = words[r][k] >> (4 * (lane & 7));
+                    total.x = __fmul_rn(__fmul_rn(total.x, (n & 1u) ? 1.0f : 0.0f), p.scale);
+                    total.y = __fmul_rn(__fmul_rn(total.y, (n & 2u) ? 1.0f : 0.0f), p.scale);
+                    total.z = __fmul_rn(__fmul_rn(total.z, (n & 4u) ? 1.0f : 0.0f), p.scale);
+                    total.w = __fmul_rn(__fmul_rn(total.w, (n & 8u) ? 1.0f : 0.0f), p.scale);
+                }
+                IO::template store<kAligned>(p.grad_branch, chunk, total);
+            }
+        }
+    }
+
+    if constexpr (kParams) {
+        // Combine the warps of this CTA in warp order (fixed order => the CTA
+        // partial is reproducible), then hand the [2, H] partial on.
+        __shared__ float4 combined[2 * kChunksPerRow];
+#pragma unroll 1
+        for (int turn = 0; turn < kWarps; ++turn) {
+            if (warp == turn) {
+#pragma unroll
+                for (int k = 0; k < V; ++k) {
+                    const int c = lane + k * kWarpSize;
+                    if (turn == 0) {
+                        combined[c] = acc_weight[k];
+                        combined[kChunksPerRow + c] = acc_bias[k];
+                    } else {
+                        float4 w = combined[c];
+                        float4 bsum = combined[kChunksPerRow + c];
+                        w.x += acc_weight[k].x;
+                        w.y += acc_weight[k].y;
+                        w.z += acc_weight[k].z;
+                        w.w += acc_weight[k].w;
+                        bsum.x += acc_bias[k].x;
+                        bsum.y += acc_bias[k].y;
+                        bsum.z += acc_bias[k].z;
+                        bsum.w += acc_bias[k].w;
+                        combined[c] = w;
+                        combined[kChunksPerRow + c] = bsum;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        if (p.deterministic) {
+            float4* out = reinterpret_cast<float4*>(p.partials)
+                + static_cast<int64_t>(blockIdx.x) * (2 * kChunksPerRow);
+            for (int c = threadIdx.x; c < 2 * kChunksPerRow; c += kWarps * kWarpSize) {
+                out[c] = combined[c];
+            }
+        } else {
+            for (int c = threadIdx.x; c < 2 * kChunksPerRow; c += kWarps * kWarpSize) {
+                const float4 v = combined[c];
+                if constexpr (kAligned) {
+                    red_add_f4(p.grad_parameters + 4 * c, v);
+                } else {
+                    atomicAdd(p.grad_parameters + 4 * c + 0, v.x);
+                    atomicAdd(p.grad_parameters + 4 * c + 1, v.y);
+                    atomicAdd(p.grad_parameters + 4 * c + 2, v.z);
+                    atomicAdd(p.grad_parameters + 4 * c + 3, v.w);
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Deterministic stage 2: out[c] = sum over CTA partials in a fixed order.
+// 32 columns x kSegments contiguous partial ranges per CTA; each range is
+// summed serially in index order, the ranges are combined in range order.
+// ---------------------------------------------------------------------------
+template <int kSegments>
+__global__ void __launch_bounds__(kSegments * kWarpSize)
+rln_reduce_partials_kernel(
+    const float* __restrict__ partials,
+    float* __restrict__ out,
+    int partial_count,
+    int columns) {
+    __shared__ float staged[kSegments][kWarpSize];
+    const int lane = threadIdx.x & (kWarpSize - 1);
+    const int segment = threadIdx.x / kWarpSize;
+    const int column = blockIdx.x * kWarpSize + lane;
+    const int per_segment = (partial_count + kSegments - 1) / kSegments;
+    const int begin = segment * per_segment;
+    const int end = min(partial_count, begin + per_segment);
+    float sum = 0.0f;
+    if (column < columns) {
+        for (int index = begin; index < end; ++index) {
+            sum += partials[static_cast<int64_t>(index) * columns + column];
+        }
+    }
+    staged[segment][lane] = sum;
+    __syncthreads();
+    if (segment == 0 && column < columns) {
+        float total = staged[0][lane];
+#pragma unroll
+        for (int s = 1; s < kSegments; ++s) {
+            total += staged[s][lane];
+        }
+        out[column] = total;
+    }
+}
+
+}  // namespace rln

@@ -1,0 +1,179 @@
+/*
+ * C ABI of the sm_100a (B200) fused residual-add + dropout + LayerNorm path.
+ *
+ * Plain pointers and sizes only: no torch, ATen or C++ types cross this
+ * boundary.  Every pointer named "device" must be a device address valid on
+ * the CUDA device that is current when the call is made; the work is enqueued
+ * on `stream` (a cudaStream_t passed as void*, NULL = the legacy default
+ * stream) and the call returns without synchronising.  No entry point
+ * allocates or frees device memory unless its comment says so.
+ *
+ * These entry points replace, one to one, the two host functions that the
+ * reference project (T-vaccari/gfx1010-kernels) exposes to its binding in
+ * csrc/residual_layer_norm.h:10-42 and implements in
+ * csrc/residual_layer_norm_kernel.hip:1720-2036.  The reference mixes tensor
+ * allocation, validation and launch in those functions; here allocation and
+ * tensor validation stay in the binding and the launch is what crosses the ABI.
+ *
+ * Return value: RLN_OK (0) or a negative RLN_ERR_* code.  Nothing throws.
+ */
+#ifndef RLN_SM100_H_
+#define RLN_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define RLN_API __attribute__((visibility("default")))
+#else
+#define RLN_API
+#endif
+
+#define RLN_OK 0
+#define RLN_ERR_NULL_POINTER (-1)       /* a required pointer is NULL */
+#define RLN_ERR_HIDDEN_SIZE (-2)        /* hidden not in {128,256,384,512,768,1024} */
+#define RLN_ERR_ROW_COUNT (-3)          /* rows <= 0 ("empty tensors are unsupported") */
+#define RLN_ERR_DROPOUT_P (-4)          /* dropout_p outside [0, 1) */
+#define RLN_ERR_EPS (-5)                /* eps <= 0 */
+#define RLN_ERR_ALIGNMENT (-6)          /* pointer not aligned to its element size */
+#define RLN_ERR_WORKSPACE (-7)          /* workspace missing or too small */
+#define RLN_ERR_CUDA (-8)               /* a CUDA runtime call failed; see rln_sm100_last_cuda_error */
+#define RLN_ERR_HOST_BUFFERS (-9)       /* host-buffer pipeline: bad chunk size or context */
+#define RLN_ERR_LIMIT (-10)             /* size beyond a documented fixed maximum */
+
+/* ABI version of this header; bumped on any signature change. */
+#define RLN_SM100_ABI_VERSION 1
+RLN_API int rln_sm100_abi_version(void);
+
+/* Human-readable text for a status code (static storage, never NULL). */
+RLN_API const char* rln_sm100_status_string(int status);
+
+/* cudaError_t value of the most recent failing CUDA call made by this library
+ * on the calling thread (0 if none). */
+RLN_API int rln_sm100_last_cuda_error(void);
+
+/*
+ * Forward: updated = x + dropout(branch); normalized = LayerNorm(updated).
+ *
+ * Replaces residual_layer_norm_forward_hip
+ * (csrc/residual_layer_norm.h:10-24, csrc/residual_layer_norm_kernel.hip:1720-1827)
+ * and the kernels it dispatches (forward kernel :425-545, vector4 kernel :353-422).
+ *
+ *   x            device, float32 [rows, hidden]
+ *   branch       device, float16 (branch_is_half != 0) or float32, [rows, hidden]
+ *   weight, bias device, float32 [hidden]
+ *   updated      device out, float32 [rows, hidden]
+ *   normalized   device out, float32 [rows, hidden]
+ *   mean, rstd   device out, float32 [rows]   (rstd = rsqrt(centred variance + eps))
+ *   dropout_mask device out, uint32 [rows * hidden/32]; bit (col & 31) of word
+ *                row*(hidden/32) + col/32 is 1 when the element was kept
+ *                (layout of :500-511).  Ignored (may be NULL) when
+ *                dropout_active == 0.
+ *   dropout_active  the caller's (training && dropout_p > 0)
+ *   seed, offset Philox4x32-10 key and per-call counter.  Element group
+ *                g = ((row_base + row) * hidden + col) / 4 uses counter
+ *                (lo32(offset), hi32(offset), lo32(g), hi32(g)), key
+ *                (lo32(seed), hi32(seed)); output word j decides column 4g+j;
+ *                keep <=> word >= (uint32)((double)dropout_p * 2^32)  (:896-899).
+ *   row_base     global index of this call's first row.  A row shard that
+ *                passes its global offset reproduces the mask of the unsharded
+ *                call bit for bit.  0 for an unsharded call.
+ *
+ * Pointers that are 16-byte aligned (8-byte for a float16 branch) take the
+ * vectorised kernels; otherwise a scalar kernel with identical results in
+ * exact arithmetic is used (the reference's alignment predicate :1084-1120).
+ */
+RLN_API int rln_sm100_forward(
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    float* updated,
+    float* normalized,
+    float* mean,
+    float* rstd,
+    uint32_t* dropout_mask,
+    int64_t rows,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    uint64_t seed,
+    uint64_t offset,
+    int64_t row_base,
+    void* stream);
+
+/*
+ * Bytes of device scratch the backward needs for the fixed-order (deterministic)
+ * parameter reduction on the current device: one [2, hidden] float32 partial
+ * per CTA of the persistent grid.  0 when deterministic == 0 or when parameter
+ * gradients are not requested.  Negative RLN_ERR_* on invalid arguments.
+ *
+ * Stands where the reference allocates its [2, ceil(rows/block_rows), hidden]
+ * partial tensor (csrc/residual_layer_norm_kernel.hip:1870-1878).
+ */
+RLN_API int64_t rln_sm100_backward_workspace_bytes(
+    int64_t rows,
+    int32_t hidden,
+    int32_t deterministic);
+
+/*
+ * Backward: grad_x, grad_branch and (optionally) grad_weight/grad_bias in one
+ * pass over the row data.
+ *
+ * Replaces residual_layer_norm_backward_hip
+ * (csrc/residual_layer_norm.h:27-42, csrc/residual_layer_norm_kernel.hip:1830-2036)
+ * and its kernels: backward-input :548-618 / :621-724, deterministic partials +
+ * reduce :727-786, atomic parameter kernels :789-869.
+ *
+ *   grad_updated, grad_normalized, updated   device, float32 [rows, hidden]
+ *   weight                                   device, float32 [hidden]
+ *   mean, rstd                               device, float32 [rows]
+ *   dropout_mask     device, uint32 [rows*hidden/32] (ignored when dropout_active == 0)
+ *   grad_x           device out, float32 [rows, hidden]
+ *   grad_branch      device out, float16 or float32 [rows, hidden]
+ *   grad_parameters  device out, float32 [2, hidden]: row 0 = grad_weight
+ *                    (sum over rows of grad_normalized * xhat), row 1 = grad_bias
+ *                    (sum over rows of grad_normalized).  NULL = not requested
+ *                    (the reference's compute_parameter_gradients == false).
+ *   deterministic    0: per-CTA shared-memory partials + fp32 atomics into
+ *                       grad_parameters (zeroed by this call on `stream`);
+ *                    1: per-CTA partials stored to `workspace`, then summed in
+ *                       CTA-index order by a second kernel.  The grid is a pure
+ *                       function of (hidden, rows, device), so two calls with
+ *                       the same inputs give bitwise-identical results.
+ *   workspace        device scratch of at least
+ *                    rln_sm100_backward_workspace_bytes(...) bytes, 16-byte
+ *                    aligned; may be NULL when that size is 0.
+ */
+RLN_API int rln_sm100_backward(
+    const float* grad_updated,
+    const float* grad_normalized,
+    const float* updated,
+    const float* weight,
+    const float* mean,
+    const float* rstd,
+    const uint32_t* dropout_mask,
+    float* grad_x,
+    void* grad_branch,
+    float* grad_parameters,
+    void* workspace,
+    int64_t workspace_bytes,
+    int64_t rows,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int32_t dropout_active,
+    float dropout_p,
+    int32_t deterministic,
+    void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif  /* RLN_SM100_H_ */

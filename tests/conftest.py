@@ -1,0 +1,68 @@
+"""Test configuration: import paths, the ``gpu`` marker and shared fixtures."""
+
+import json
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+REPO = Path(__file__).resolve().parent.parent
+PACKAGE_ROOT = REPO / "gfx1010-kernels_b200"
+for path in (str(REPO), str(PACKAGE_ROOT), str(Path(__file__).resolve().parent)):
+    if path not in sys.path:
+        sys.path.insert(0, path)
+
+
+def pytest_configure(config):
+    config.addinivalue_line(
+        "markers", "gpu: needs a CUDA device of compute capability 10.x (B200)"
+    )
+
+
+def pytest_collection_modifyitems(config, items):
+    """GPU tests fail (not skip) on a GPU box whose native backend is broken;
+    without any CUDA device they are skipped."""
+    import torch
+
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session", autouse=True)
+def built_libraries():
+    """Build the in-tree libraries when they are missing (nvcc cross-compiles
+    without a GPU).  An existing build is used as is."""
+    import build as rln_build
+
+    if not (rln_build.KERNEL_LIBRARY.exists() and rln_build.EXTENSION.exists()):
+        rln_build.build_all()
+    return rln_build.KERNEL_LIBRARY, rln_build.EXTENSION
+
+
+@pytest.fixture(scope="session")
+def golden_cases():
+    """name -> dict of numpy arrays + the case's metadata."""
+    directory = REPO / "tests" / "golden"
+    meta = json.loads((directory / "rln_cases.json").read_text())["cases"]
+    arrays = np.load(directory / "rln_cases.npz")
+    cases = {}
+    for entry in meta:
+        name = entry["name"]
+        record = {
+            key.split("/", 1)[1]: arrays[key]
+            for key in arrays.files
+            if key.startswith(name + "/")
+        }
+        record["meta"] = entry
+        cases[name] = record
+    return cases
+
+
+@pytest.fixture(scope="session")
+def philox_kat():
+    return json.loads((REPO / "tests" / "golden" / "philox_kat.json").read_text())
