@@ -63,6 +63,23 @@ def _cuda_home() -> Path:
     return Path(nvcc).resolve().parent.parent
 
 
+def _host_compiler() -> str:
+    """The system g++ (the one nvcc also uses as its host compiler).
+
+    ``$CXX`` is deliberately not consulted: a wrapper that links libstdc++
+    statically gives the extension a second, uninitialised copy of the iostream
+    locale machinery next to the one torch uses, and formatting a number into an
+    error message then crashes.  ``RLN_CXX`` overrides for unusual setups.
+    """
+    override = os.environ.get("RLN_CXX")
+    if override:
+        return override
+    for candidate in ("/usr/bin/g++", shutil.which("g++")):
+        if candidate and Path(candidate).exists():
+            return candidate
+    raise RuntimeError("g++ was not found")
+
+
 def _newer(target: Path, sources) -> bool:
     if not target.exists():
         return False
@@ -138,7 +155,7 @@ def build_extension(force=False, verbose=False) -> Path:
         includes += ["-isystem", path]
     includes += ["-isystem", sysconfig.get_paths()["include"], "-isystem", cuda / "include"]
     command = [
-        os.environ.get("CXX", "g++"),
+        _host_compiler(),
         "-O2",
         "-std=c++17",
         "-fPIC",
@@ -166,7 +183,21 @@ def build_extension(force=False, verbose=False) -> Path:
         f"-Wl,-rpath,{torch_library}",
     ]
     _run(command, verbose)
+    _check_dynamic_libstdcxx(EXTENSION)
     return EXTENSION
+
+
+def _check_dynamic_libstdcxx(library: Path) -> None:
+    """Refuse an extension that carries its own copy of libstdc++."""
+    listing = subprocess.run(
+        ["nm", "-D", "--defined-only", str(library)], capture_output=True, text=True
+    ).stdout
+    if "_ZNSt6locale5facet" in listing:
+        library.unlink()
+        raise RuntimeError(
+            f"{library.name} was linked with a static libstdc++; "
+            "set RLN_CXX to a compiler that links it dynamically"
+        )
 
 
 def build_all(force=False, verbose=False):
