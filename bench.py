@@ -336,7 +336,8 @@ def run_native_arm(args, rank, local_rank, world):
     # warm-up: at least W steps and long enough for the clock sampler to see load
     warm_begin = time.perf_counter()
     done = 0
-    while done < max(args.warmup, 3) or (time.perf_counter() - warm_begin < 1.0 and done < 5000):
+    settle = 0.0 if args.kernel_only else 1.0
+    while done < max(args.warmup, 3) or (time.perf_counter() - warm_begin < settle and done < 5000):
         step(done, False)
         done += 1
         if done % 50 == 0:
@@ -362,9 +363,12 @@ def run_native_arm(args, rank, local_rank, world):
         clocks["window"] = "warm-up + timed region (timed region shorter than the sampling interval)"
 
     # end-to-end: pinned host inputs -> device -> public API fwd+bwd -> results back to host
-    e2e = run_end_to_end(
-        args, device, host, weight, bias, dropout_p, world, residual_layer_norm
-    )
+    if args.kernel_only:
+        e2e = {"ms": float("nan"), "steps": 0, "h2d": 0, "d2h": 0}
+    else:
+        e2e = run_end_to_end(
+            args, device, host, weight, bias, dropout_p, world, residual_layer_norm
+        )
     sampler.stop()
 
     if world > 1:
@@ -385,7 +389,7 @@ def run_native_arm(args, rank, local_rank, world):
         bwd_gbs = bwd_bytes / (backward_ms * 1e-3) / 1e9
         step_gbs = (fwd_bytes + bwd_bytes) * world * args.steps / (elapsed_ms * 1e-3) / 1e9
         cpu = None
-        if world == 1:
+        if world == 1 and not args.kernel_only:
             sample_rows = min(rows, CPU_SAMPLE_ROWS)
             times, threads = time_cpu_reference(sample_rows, hidden, branch_dtype, dropout_p, 5, 1)
             cpu = {
@@ -432,7 +436,7 @@ def run_native_arm(args, rank, local_rank, world):
                 "traffic": None,
             },
             "cpu_baseline": cpu,
-            "e2e": {
+            "e2e": None if args.kernel_only else {
                 "value": total_rows * e2e["steps"] / (e2e_ms * 1e-3),
                 "unit": UNIT,
                 "h2d_bytes_per_step": e2e["h2d"],
@@ -518,6 +522,13 @@ def main(argv=None):
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="h768_64Mi")
+    parser.add_argument(
+        "--kernel-only",
+        action="store_true",
+        help="profiling mode: exactly W warm-up steps, no clock-settling warm-up, no "
+             "end-to-end leg and no CPU baseline (few launches, so that a profiler "
+             "capture of this command ends quickly)",
+    )
     args = parser.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
