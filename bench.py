@@ -350,11 +350,15 @@ def run_native_arm(args, rank, local_rank, world):
     stop = torch.cuda.Event(enable_timing=True)
     start.record()
     for index in range(args.steps):
-        step(warmup_actual + index, True)
+        step(warmup_actual + index, not args.no_kernel_events)
     stop.record()
     fence()
     timed_end = time.perf_counter()
     elapsed_ms = start.elapsed_time(stop)
+    if args.no_kernel_events:
+        for index in range(min(args.steps, 50)):
+            step(warmup_actual + args.steps + index, True)
+        torch.cuda.synchronize()
     forward_ms = statistics.mean(a.elapsed_time(b) for a, b in forward_events)
     backward_ms = statistics.mean(a.elapsed_time(b) for a, b in backward_events)
     clocks = sampler.summary(timed_begin, timed_end)
@@ -522,6 +526,12 @@ def main(argv=None):
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="h768_64Mi")
+    parser.add_argument(
+        "--no-kernel-events",
+        action="store_true",
+        help="do not record per-kernel CUDA events inside the timed steps "
+             "(the roofline entry is then taken from a separate pass)",
+    )
     parser.add_argument(
         "--kernel-only",
         action="store_true",

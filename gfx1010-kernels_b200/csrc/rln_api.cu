@@ -149,12 +149,18 @@ extern "C" int rln_sm100_forward(
     params.offset_lo = static_cast<uint32_t>(offset);
     params.offset_hi = static_cast<uint32_t>(offset >> 32);
 
+    int sm_count = 0;
+    const int status = current_sm_count(&sm_count);
+    if (status != RLN_OK) {
+        return status;
+    }
     const cudaError_t error = rln::launch_forward(
         hidden,
         branch_is_half != 0,
         dropout_active != 0,
         vector_ok,
         params,
+        sm_count,
         static_cast<cudaStream_t>(stream));
     return error == cudaSuccess ? RLN_OK : cuda_failed(error);
 }

@@ -17,7 +17,8 @@ template <int H, typename BranchT, bool kDropout, bool kParams, bool kAligned>
 cudaError_t launch_backward_typed(const BackwardParams& params, int grid, cudaStream_t stream) {
     constexpr int kWarps = BackwardTune<H>::kWarps;
     constexpr int kRows = BackwardTune<H>::kRows;
-    rln_backward_kernel<H, BranchT, kDropout, kParams, kAligned, kWarps, kRows>
+    rln_backward_kernel<H, BranchT, kDropout, kParams, kAligned, kWarps, kRows,
+                        BackwardTune<H>::kCtasPerSm>
         <<<static_cast<unsigned>(grid), kWarps * kWarpSize, 0, stream>>>(params);
     return cudaGetLastError();
 }

@@ -5,15 +5,20 @@ namespace rln {
 namespace {
 
 template <int H, typename BranchT, bool kDropout, bool kAligned>
-cudaError_t launch_forward_typed(const ForwardParams& params, cudaStream_t stream) {
+cudaError_t launch_forward_typed(const ForwardParams& params, int sm_count, cudaStream_t stream) {
     constexpr int kWarps = ForwardTune<H>::kWarps;
     constexpr int kRows = ForwardTune<H>::kRows;
+    constexpr int kMinCtas = ForwardTune<H>::kMinCtas;
     constexpr int64_t kRowsPerCta = static_cast<int64_t>(kWarps) * kRows;
     int64_t blocks = (params.rows + kRowsPerCta - 1) / kRowsPerCta;
+    if (ForwardTune<H>::kPersistent) {
+        const int64_t resident = static_cast<int64_t>(sm_count) * kMinCtas;
+        blocks = blocks < resident ? blocks : resident;
+    }
     if (blocks > 0x7fffffff) {
         blocks = 0x7fffffff;  // the kernel grid-strides over the remainder
     }
-    rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows>
+    rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows, kMinCtas>
         <<<static_cast<unsigned>(blocks), kWarps * kWarpSize, 0, stream>>>(params);
     return cudaGetLastError();
 }
@@ -24,13 +29,14 @@ cudaError_t launch_forward_hidden(
     bool dropout,
     bool aligned,
     const ForwardParams& params,
+    int sm_count,
     cudaStream_t stream) {
 #define RLN_FWD_CASE(HALF, DROP, ALIGNED)                                                   \
     if (branch_is_half == HALF && dropout == DROP && aligned == ALIGNED) {                  \
         if constexpr (HALF) {                                                               \
-            return launch_forward_typed<H, __half, DROP, ALIGNED>(params, stream);          \
+            return launch_forward_typed<H, __half, DROP, ALIGNED>(params, sm_count, stream);          \
         } else {                                                                            \
-            return launch_forward_typed<H, float, DROP, ALIGNED>(params, stream);           \
+            return launch_forward_typed<H, float, DROP, ALIGNED>(params, sm_count, stream);           \
         }                                                                                   \
     }
     RLN_FWD_CASE(true, true, true)
@@ -53,14 +59,15 @@ cudaError_t launch_forward(
     bool dropout,
     bool aligned,
     const ForwardParams& params,
+    int sm_count,
     cudaStream_t stream) {
     switch (hidden) {
-        case 128: return launch_forward_hidden<128>(branch_is_half, dropout, aligned, params, stream);
-        case 256: return launch_forward_hidden<256>(branch_is_half, dropout, aligned, params, stream);
-        case 384: return launch_forward_hidden<384>(branch_is_half, dropout, aligned, params, stream);
-        case 512: return launch_forward_hidden<512>(branch_is_half, dropout, aligned, params, stream);
-        case 768: return launch_forward_hidden<768>(branch_is_half, dropout, aligned, params, stream);
-        case 1024: return launch_forward_hidden<1024>(branch_is_half, dropout, aligned, params, stream);
+        case 128: return launch_forward_hidden<128>(branch_is_half, dropout, aligned, params, sm_count, stream);
+        case 256: return launch_forward_hidden<256>(branch_is_half, dropout, aligned, params, sm_count, stream);
+        case 384: return launch_forward_hidden<384>(branch_is_half, dropout, aligned, params, sm_count, stream);
+        case 512: return launch_forward_hidden<512>(branch_is_half, dropout, aligned, params, sm_count, stream);
+        case 768: return launch_forward_hidden<768>(branch_is_half, dropout, aligned, params, sm_count, stream);
+        case 1024: return launch_forward_hidden<1024>(branch_is_half, dropout, aligned, params, sm_count, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -73,6 +73,30 @@ struct BackwardParams {
 };
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch (sm_90+).  Every kernel first allows the next
+// kernel of the stream to be scheduled while this one drains, then waits until
+// the previous kernel has completed and its writes are visible.  Both are
+// no-ops for a launch without the programmatic-serialization attribute.
+// Nothing is read or written before the wait, so any predecessor is safe.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Zeroes a small buffer; stands in for cudaMemsetAsync so that the kernel
+// chain of a training step stays kernel -> kernel (a memset node would break
+// the programmatic dependency between the forward and the backward).
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
+rln_zero_kernel(float4* __restrict__ out, int count4) {
+    grid_dependency_sync();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < count4; i += gridDim.x * blockDim.x) {
+        out[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Philox4x32-10 (Salmon et al., SC'11), written out; one call = 4 random words.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint4 philox4x32_10(uint4 counter, uint32_t key0, uint32_t key1) {
@@ -287,6 +311,7 @@ rln_forward_kernel(const ForwardParams p) {
     const int lane = threadIdx.x & (kWarpSize - 1);
     const int warp = threadIdx.x / kWarpSize;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRows;
+    grid_dependency_sync();
 
     for (int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRows;
          first < p.rows; first += stride) {
@@ -437,6 +462,8 @@ rln_backward_kernel(const BackwardParams p) {
     const int lane = threadIdx.x & (kWarpSize - 1);
     const int warp = threadIdx.x / kWarpSize;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRows;
+
+    grid_dependency_sync();
 
     float4 acc_weight[kParams ? V : 1];
     float4 acc_bias[kParams ? V : 1];
@@ -612,6 +639,7 @@ rln_reduce_partials_kernel(
     const int lane = threadIdx.x & (kWarpSize - 1);
     const int segment = threadIdx.x / kWarpSize;
     const int column = blockIdx.x * kWarpSize + lane;
+    grid_dependency_sync();
     const int per_segment = (partial_count + kSegments - 1) / kSegments;
     const int begin = segment * per_segment;
     const int end = min(partial_count, begin + per_segment);

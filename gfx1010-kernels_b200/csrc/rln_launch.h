@@ -9,22 +9,39 @@
 
 namespace rln {
 
-// Compile-time launch geometry per hidden size.  kWarps warps per CTA, each
-// warp handles kRows consecutive rows per loop iteration (more rows in flight
-// for narrow rows).  kCtasPerSm sizes the persistent backward grid; it is a
-// constant (not an occupancy query) so that the deterministic partial layout
-// depends only on (hidden, rows, SM count).
+// Compile-time launch geometry per hidden size, chosen from measurements on
+// B200 (87,381 x 768 and equal-volume shapes of the other widths):
+//   kWarps    warps per CTA;
+//   kRows     consecutive rows a warp keeps in flight per loop iteration;
+//   kMinCtas  __launch_bounds__ minimum, i.e. the register budget
+//             65536 / (32 * kWarps * kMinCtas) per thread.  About 16 resident
+//             warps per SM (more for narrow rows) is the sweet spot for the
+//             forward: fewer warps leave HBM latency exposed, more warps cut
+//             the registers a warp can keep in flight;
+//   kPersistent (forward) launch exactly sm_count * kMinCtas CTAs that
+//             grid-stride, instead of one CTA per kWarps * kRows rows.  Only
+//             pays for the narrowest rows, where a CTA would otherwise live
+//             for a single 512-byte row per warp.
 template <int H>
 struct ForwardTune {
-    static constexpr int kWarps = 4;
-    static constexpr int kRows = H <= 128 ? 4 : (H <= 256 ? 2 : 1);
+    static constexpr int kWarps = H <= 128 ? 8 : 4;
+    static constexpr int kRows = 1;
+    static constexpr int kMinCtas =
+        H <= 128 ? 6 : (H <= 384 ? 8 : (H <= 512 ? 6 : 4));
+    static constexpr bool kPersistent = H <= 128;
 };
 
+// The backward grid is persistent (register-resident parameter-gradient
+// accumulators): exactly sm_count * kCtasPerSm CTAs, all resident because
+// kCtasPerSm is also the __launch_bounds__ minimum.  It is a constant (not an
+// occupancy query) so that the deterministic partial layout depends only on
+// (hidden, rows, SM count).
 template <int H>
 struct BackwardTune {
     static constexpr int kWarps = 4;
-    static constexpr int kRows = H <= 128 ? 4 : (H <= 256 ? 2 : 1);
-    static constexpr int kCtasPerSm = H <= 512 ? 6 : (H <= 768 ? 4 : 3);
+    static constexpr int kRows = (H == 128 || H == 384) ? 2 : 1;
+    static constexpr int kCtasPerSm =
+        H <= 128 ? 5 : (H <= 256 ? 6 : (H <= 384 ? 2 : (H <= 512 ? 3 : 2)));
 };
 
 // Number of CTAs of the persistent backward grid (pure function of its
@@ -37,6 +54,7 @@ cudaError_t launch_forward(
     bool dropout,
     bool aligned,
     const ForwardParams& params,
+    int sm_count,
     cudaStream_t stream);
 
 cudaError_t launch_backward(
