@@ -15,6 +15,12 @@ int cuda_failed(cudaError_t error) {
     return RLN_ERR_CUDA;
 }
 
+}  // namespace
+
+int rln::record_cuda_error(cudaError_t error) { return cuda_failed(error); }
+
+namespace {
+
 bool supported_hidden(int32_t hidden) {
     return hidden == 128 || hidden == 256 || hidden == 384 || hidden == 512
         || hidden == 768 || hidden == 1024;

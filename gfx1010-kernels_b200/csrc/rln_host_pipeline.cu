@@ -1,0 +1,329 @@
+// Host-buffer pipeline of the residual LayerNorm training step: chunked
+// host->device copies, forward + backward kernels and device->host copies on
+// three streams, so that both PCIe directions and the SMs work at once.
+#include "rln_sm100.h"
+
+#include <cuda_runtime.h>
+
+#include <new>
+
+#include "rln_launch.h"
+
+namespace {
+
+constexpr int kMaxDepth = 8;
+
+// total = first ? slot : total + slot, over 2 * hidden floats.  Chunks are
+// accumulated in chunk order on one stream, so the sum order is fixed.
+__global__ void accumulate_parameters_kernel(
+    float* __restrict__ total,
+    const float* __restrict__ slot,
+    int count,
+    int first) {
+    const int index = blockIdx.x * blockDim.x + threadIdx.x;
+    if (index < count) {
+        total[index] = first ? slot[index] : total[index] + slot[index];
+    }
+}
+
+struct Slot {
+    float* x = nullptr;
+    void* branch = nullptr;
+    float* grad_updated = nullptr;
+    float* grad_normalized = nullptr;
+    float* updated = nullptr;
+    float* normalized = nullptr;
+    float* grad_x = nullptr;
+    void* grad_branch = nullptr;
+    float* mean = nullptr;
+    float* rstd = nullptr;
+    uint32_t* mask = nullptr;
+    float* grad_parameters = nullptr;
+    void* workspace = nullptr;
+    cudaEvent_t in_ready = nullptr;   // inputs of the slot have arrived
+    cudaEvent_t computed = nullptr;   // kernels of the slot are done (inputs reusable)
+    cudaEvent_t drained = nullptr;    // outputs of the slot have left (outputs reusable)
+    bool used = false;
+};
+
+}  // namespace
+
+struct RlnHostPipeline {
+    int device = 0;
+    int32_t hidden = 0;
+    int32_t branch_is_half = 0;
+    int64_t chunk_rows = 0;
+    int32_t depth = 0;
+    int64_t workspace_bytes = 0;
+    cudaStream_t stream_in = nullptr;
+    cudaStream_t stream_compute = nullptr;
+    cudaStream_t stream_out = nullptr;
+    float* weight = nullptr;
+    float* bias = nullptr;
+    float* total = nullptr;
+    Slot slots[kMaxDepth];
+};
+
+namespace {
+
+void release(RlnHostPipeline* p) {
+    if (p == nullptr) {
+        return;
+    }
+    for (int s = 0; s < kMaxDepth; ++s) {
+        Slot& slot = p->slots[s];
+        cudaFree(slot.x);
+        cudaFree(slot.branch);
+        cudaFree(slot.grad_updated);
+        cudaFree(slot.grad_normalized);
+        cudaFree(slot.updated);
+        cudaFree(slot.normalized);
+        cudaFree(slot.grad_x);
+        cudaFree(slot.grad_branch);
+        cudaFree(slot.mean);
+        cudaFree(slot.rstd);
+        cudaFree(slot.mask);
+        cudaFree(slot.grad_parameters);
+        cudaFree(slot.workspace);
+        if (slot.in_ready) cudaEventDestroy(slot.in_ready);
+        if (slot.computed) cudaEventDestroy(slot.computed);
+        if (slot.drained) cudaEventDestroy(slot.drained);
+    }
+    cudaFree(p->weight);
+    cudaFree(p->bias);
+    cudaFree(p->total);
+    if (p->stream_in) cudaStreamDestroy(p->stream_in);
+    if (p->stream_compute) cudaStreamDestroy(p->stream_compute);
+    if (p->stream_out) cudaStreamDestroy(p->stream_out);
+    delete p;
+}
+
+#define RLN_TRY(call)                      \
+    do {                                   \
+        if ((call) != cudaSuccess) {       \
+            return false;                  \
+        }                                  \
+    } while (0)
+
+bool allocate(RlnHostPipeline* p) {
+    const size_t elements = static_cast<size_t>(p->chunk_rows) * p->hidden;
+    const size_t branch_bytes = elements * (p->branch_is_half ? 2 : 4);
+    RLN_TRY(cudaStreamCreateWithFlags(&p->stream_in, cudaStreamNonBlocking));
+    RLN_TRY(cudaStreamCreateWithFlags(&p->stream_compute, cudaStreamNonBlocking));
+    RLN_TRY(cudaStreamCreateWithFlags(&p->stream_out, cudaStreamNonBlocking));
+    RLN_TRY(cudaMalloc(&p->weight, p->hidden * sizeof(float)));
+    RLN_TRY(cudaMalloc(&p->bias, p->hidden * sizeof(float)));
+    RLN_TRY(cudaMalloc(&p->total, 2 * p->hidden * sizeof(float)));
+    for (int s = 0; s < p->depth; ++s) {
+        Slot& slot = p->slots[s];
+        RLN_TRY(cudaMalloc(&slot.x, elements * 4));
+        RLN_TRY(cudaMalloc(&slot.branch, branch_bytes));
+        RLN_TRY(cudaMalloc(&slot.grad_updated, elements * 4));
+        RLN_TRY(cudaMalloc(&slot.grad_normalized, elements * 4));
+        RLN_TRY(cudaMalloc(&slot.updated, elements * 4));
+        RLN_TRY(cudaMalloc(&slot.normalized, elements * 4));
+        RLN_TRY(cudaMalloc(&slot.grad_x, elements * 4));
+        RLN_TRY(cudaMalloc(&slot.grad_branch, branch_bytes));
+        RLN_TRY(cudaMalloc(&slot.mean, p->chunk_rows * sizeof(float)));
+        RLN_TRY(cudaMalloc(&slot.rstd, p->chunk_rows * sizeof(float)));
+        RLN_TRY(cudaMalloc(&slot.mask, elements / 8));
+        RLN_TRY(cudaMalloc(&slot.grad_parameters, 2 * p->hidden * sizeof(float)));
+        if (p->workspace_bytes > 0) {
+            RLN_TRY(cudaMalloc(&slot.workspace, p->workspace_bytes));
+        }
+        RLN_TRY(cudaEventCreateWithFlags(&slot.in_ready, cudaEventDisableTiming));
+        RLN_TRY(cudaEventCreateWithFlags(&slot.computed, cudaEventDisableTiming));
+        RLN_TRY(cudaEventCreateWithFlags(&slot.drained, cudaEventDisableTiming));
+    }
+    return true;
+}
+
+}  // namespace
+
+extern "C" int rln_sm100_host_pipeline_create(
+    RlnHostPipeline** pipeline,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int64_t chunk_rows,
+    int32_t depth) {
+    if (pipeline == nullptr) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    *pipeline = nullptr;
+    if (chunk_rows <= 0 || chunk_rows > (1 << 24) || depth < 2 || depth > kMaxDepth) {
+        return RLN_ERR_HOST_BUFFERS;
+    }
+    // the deterministic workspace for the largest chunk; also validates hidden
+    const int64_t workspace_bytes = rln_sm100_backward_workspace_bytes(chunk_rows, hidden, 1);
+    if (workspace_bytes < 0) {
+        return static_cast<int>(workspace_bytes);
+    }
+    RlnHostPipeline* p = new (std::nothrow) RlnHostPipeline();
+    if (p == nullptr) {
+        return RLN_ERR_HOST_BUFFERS;
+    }
+    const cudaError_t device_error = cudaGetDevice(&p->device);
+    if (device_error != cudaSuccess) {
+        delete p;
+        return rln::record_cuda_error(device_error);
+    }
+    p->hidden = hidden;
+    p->branch_is_half = branch_is_half ? 1 : 0;
+    p->chunk_rows = chunk_rows;
+    p->depth = depth;
+    p->workspace_bytes = workspace_bytes;
+    if (!allocate(p)) {
+        release(p);
+        return rln::record_cuda_error(cudaGetLastError());
+    }
+    *pipeline = p;
+    return RLN_OK;
+}
+
+extern "C" int rln_sm100_host_pipeline_destroy(RlnHostPipeline* pipeline) {
+    if (pipeline == nullptr) {
+        return RLN_OK;
+    }
+    cudaStreamSynchronize(pipeline->stream_in);
+    cudaStreamSynchronize(pipeline->stream_compute);
+    cudaStreamSynchronize(pipeline->stream_out);
+    release(pipeline);
+    return RLN_OK;
+}
+
+#undef RLN_TRY
+#define RLN_TRY(call)                                  \
+    do {                                               \
+        const cudaError_t rln_try_error = (call);      \
+        if (rln_try_error != cudaSuccess) {            \
+            return rln::record_cuda_error(rln_try_error); \
+        }                                              \
+    } while (0)
+
+extern "C" int rln_sm100_host_forward_backward(
+    RlnHostPipeline* p,
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    const float* grad_updated,
+    const float* grad_normalized,
+    float* updated,
+    float* normalized,
+    float* grad_x,
+    void* grad_branch,
+    float* grad_parameters,
+    int64_t rows,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    uint64_t seed,
+    uint64_t offset,
+    int64_t row_base,
+    int32_t deterministic) {
+    if (p == nullptr || x == nullptr || branch == nullptr || weight == nullptr || bias == nullptr
+        || grad_updated == nullptr || grad_normalized == nullptr || updated == nullptr
+        || normalized == nullptr || grad_x == nullptr || grad_branch == nullptr
+        || grad_parameters == nullptr) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    if (rows <= 0) {
+        return RLN_ERR_ROW_COUNT;
+    }
+    if (!(dropout_p >= 0.0f && dropout_p < 1.0f)) {
+        return RLN_ERR_DROPOUT_P;
+    }
+    if (!(eps > 0.0f)) {
+        return RLN_ERR_EPS;
+    }
+    int device = -1;
+    RLN_TRY(cudaGetDevice(&device));
+    if (device != p->device) {
+        return RLN_ERR_HOST_BUFFERS;
+    }
+    const int64_t hidden = p->hidden;
+    const size_t branch_element = p->branch_is_half ? 2 : 4;
+    const char* branch_bytes = static_cast<const char*>(branch);
+    char* grad_branch_bytes = static_cast<char*>(grad_branch);
+
+    for (int s = 0; s < p->depth; ++s) {
+        p->slots[s].used = false;
+    }
+    RLN_TRY(cudaMemcpyAsync(
+        p->weight, weight, hidden * sizeof(float), cudaMemcpyHostToDevice, p->stream_compute));
+    RLN_TRY(cudaMemcpyAsync(
+        p->bias, bias, hidden * sizeof(float), cudaMemcpyHostToDevice, p->stream_compute));
+
+    int64_t chunk_index = 0;
+    for (int64_t begin = 0; begin < rows; begin += p->chunk_rows, ++chunk_index) {
+        const int64_t count = rows - begin < p->chunk_rows ? rows - begin : p->chunk_rows;
+        const size_t elements = static_cast<size_t>(count) * hidden;
+        const size_t first = static_cast<size_t>(begin) * hidden;
+        Slot& slot = p->slots[chunk_index % p->depth];
+
+        // copy in (the slot's inputs are free once its previous kernels ran)
+        if (slot.used) {
+            RLN_TRY(cudaStreamWaitEvent(p->stream_in, slot.computed, 0));
+        }
+        RLN_TRY(cudaMemcpyAsync(
+            slot.x, x + first, elements * 4, cudaMemcpyHostToDevice, p->stream_in));
+        RLN_TRY(cudaMemcpyAsync(
+            slot.branch, branch_bytes + first * branch_element, elements * branch_element,
+            cudaMemcpyHostToDevice, p->stream_in));
+        RLN_TRY(cudaMemcpyAsync(
+            slot.grad_updated, grad_updated + first, elements * 4, cudaMemcpyHostToDevice,
+            p->stream_in));
+        RLN_TRY(cudaMemcpyAsync(
+            slot.grad_normalized, grad_normalized + first, elements * 4, cudaMemcpyHostToDevice,
+            p->stream_in));
+        RLN_TRY(cudaEventRecord(slot.in_ready, p->stream_in));
+
+        // compute (the slot's outputs are free once its previous results left)
+        RLN_TRY(cudaStreamWaitEvent(p->stream_compute, slot.in_ready, 0));
+        if (slot.used) {
+            RLN_TRY(cudaStreamWaitEvent(p->stream_compute, slot.drained, 0));
+        }
+        int status = rln_sm100_forward(
+            slot.x, slot.branch, p->weight, p->bias, slot.updated, slot.normalized, slot.mean,
+            slot.rstd, slot.mask, count, p->hidden, p->branch_is_half, dropout_active, dropout_p,
+            eps, seed, offset, row_base + begin, p->stream_compute);
+        if (status != RLN_OK) {
+            return status;
+        }
+        status = rln_sm100_backward(
+            slot.grad_updated, slot.grad_normalized, slot.updated, p->weight, slot.mean,
+            slot.rstd, slot.mask, slot.grad_x, slot.grad_branch, slot.grad_parameters,
+            slot.workspace, p->workspace_bytes, count, p->hidden, p->branch_is_half,
+            dropout_active, dropout_p, deterministic, p->stream_compute);
+        if (status != RLN_OK) {
+            return status;
+        }
+        const int parameter_count = static_cast<int>(2 * hidden);
+        accumulate_parameters_kernel<<<(parameter_count + 255) / 256, 256, 0, p->stream_compute>>>(
+            p->total, slot.grad_parameters, parameter_count, chunk_index == 0 ? 1 : 0);
+        RLN_TRY(cudaGetLastError());
+        RLN_TRY(cudaEventRecord(slot.computed, p->stream_compute));
+
+        // copy out
+        RLN_TRY(cudaStreamWaitEvent(p->stream_out, slot.computed, 0));
+        RLN_TRY(cudaMemcpyAsync(
+            updated + first, slot.updated, elements * 4, cudaMemcpyDeviceToHost, p->stream_out));
+        RLN_TRY(cudaMemcpyAsync(
+            normalized + first, slot.normalized, elements * 4, cudaMemcpyDeviceToHost,
+            p->stream_out));
+        RLN_TRY(cudaMemcpyAsync(
+            grad_x + first, slot.grad_x, elements * 4, cudaMemcpyDeviceToHost, p->stream_out));
+        RLN_TRY(cudaMemcpyAsync(
+            grad_branch_bytes + first * branch_element, slot.grad_branch,
+            elements * branch_element, cudaMemcpyDeviceToHost, p->stream_out));
+        RLN_TRY(cudaEventRecord(slot.drained, p->stream_out));
+        slot.used = true;
+    }
+    RLN_TRY(cudaMemcpyAsync(
+        grad_parameters, p->total, 2 * hidden * sizeof(float), cudaMemcpyDeviceToHost,
+        p->stream_compute));
+    RLN_TRY(cudaStreamSynchronize(p->stream_in));
+    RLN_TRY(cudaStreamSynchronize(p->stream_compute));
+    RLN_TRY(cudaStreamSynchronize(p->stream_out));
+    return RLN_OK;
+}

@@ -44,6 +44,10 @@ struct BackwardTune {
         H <= 128 ? 5 : (H <= 256 ? 6 : (H <= 384 ? 2 : (H <= 512 ? 3 : 2)));
 };
 
+// Remembers a failing CUDA call for rln_sm100_last_cuda_error (per thread) and
+// returns RLN_ERR_CUDA.
+int record_cuda_error(cudaError_t error);
+
 // Number of CTAs of the persistent backward grid (pure function of its
 // arguments; also the number of [2, hidden] partials in deterministic mode).
 int backward_grid(int hidden, int64_t rows, int sm_count);

@@ -1,0 +1,180 @@
+"""Training step over HOST-resident rows: chunked copy-in / compute / copy-out.
+
+``HostPipeline`` drives the ``rln_sm100_host_*`` entry points of
+``librln_sm100.so`` (declared in ``include/rln_sm100.h``) through ctypes.  It is
+the call to use when activations live in host memory (offloaded or produced on
+the CPU): instead of one copy in, the kernels, and one copy out, rows are cut
+into chunks and the three stages overlap on separate streams.
+
+The reference project has no host-buffer entry; this module is an addition on
+the caller side of the path.  Its results are those of
+``_C.residual_layer_norm_forward`` + ``_C.residual_layer_norm_backward`` on the
+same rows with the same Philox ``(seed, offset)``.
+
+There is no CPU fallback: without a CUDA device or without the native library
+the constructor raises.
+"""
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+_LIBRARY_PATH = Path(__file__).resolve().parent / "librln_sm100.so"
+_library = None
+
+_ptr = ctypes.c_void_p
+
+
+def _load():
+    global _library
+    if _library is None:
+        if not _LIBRARY_PATH.exists():
+            raise RuntimeError(f"native kernel library is missing: {_LIBRARY_PATH}")
+        lib = ctypes.CDLL(str(_LIBRARY_PATH))
+        lib.rln_sm100_status_string.restype = ctypes.c_char_p
+        lib.rln_sm100_status_string.argtypes = [ctypes.c_int]
+        lib.rln_sm100_host_pipeline_create.restype = ctypes.c_int
+        lib.rln_sm100_host_pipeline_create.argtypes = [
+            ctypes.POINTER(_ptr), ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32,
+        ]
+        lib.rln_sm100_host_pipeline_destroy.restype = ctypes.c_int
+        lib.rln_sm100_host_pipeline_destroy.argtypes = [_ptr]
+        lib.rln_sm100_host_forward_backward.restype = ctypes.c_int
+        lib.rln_sm100_host_forward_backward.argtypes = (
+            [_ptr] * 12
+            + [ctypes.c_int64, ctypes.c_int32, ctypes.c_float, ctypes.c_float,
+               ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int64, ctypes.c_int32]
+        )
+        _library = lib
+    return _library
+
+
+def _check(status, what):
+    if status != 0:
+        text = _load().rln_sm100_status_string(status).decode()
+        raise RuntimeError(f"{what} failed: {text}")
+
+
+class HostPipeline:
+    """Device staging buffers, streams and events for one (hidden, branch dtype).
+
+    ``chunk_rows`` rows are in flight per stage and ``depth`` chunks are
+    buffered (device memory: about ``depth * chunk_rows * hidden * 30`` bytes).
+    One call at a time per pipeline.
+    """
+
+    def __init__(self, hidden, branch_dtype=torch.float16, chunk_rows=8192, depth=3, device=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("HostPipeline needs a CUDA device; there is no CPU fallback")
+        if branch_dtype not in (torch.float16, torch.float32):
+            raise ValueError("branch must use float16 or float32")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
+            else torch.device(device)
+        self.hidden = int(hidden)
+        self.branch_dtype = branch_dtype
+        self.chunk_rows = int(chunk_rows)
+        self.depth = int(depth)
+        self._handle = _ptr()
+        with torch.cuda.device(self.device):
+            torch.cuda.current_stream()  # make sure the device's context exists
+            status = _load().rln_sm100_host_pipeline_create(
+                ctypes.byref(self._handle), self.hidden,
+                int(branch_dtype == torch.float16), self.chunk_rows, self.depth,
+            )
+        _check(status, "rln_sm100_host_pipeline_create")
+
+    def close(self):
+        if getattr(self, "_handle", None):
+            with torch.cuda.device(self.device):
+                _load().rln_sm100_host_pipeline_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def allocate_outputs(self, shape, pinned=True):
+        """Host tensors for ``(updated, normalized, grad_x, grad_branch, grad_parameters)``."""
+        def host(size, dtype):
+            return torch.empty(size, dtype=dtype, pin_memory=pinned)
+
+        return (
+            host(shape, torch.float32),
+            host(shape, torch.float32),
+            host(shape, torch.float32),
+            host(shape, self.branch_dtype),
+            host((2, self.hidden), torch.float32),
+        )
+
+    def forward_backward(
+        self,
+        x,
+        branch,
+        weight,
+        bias,
+        grad_updated,
+        grad_normalized,
+        dropout_p=0.0,
+        eps=1e-5,
+        training=True,
+        *,
+        seed=0,
+        offset=0,
+        row_base=0,
+        deterministic=False,
+        out=None,
+    ):
+        """One forward + backward over host tensors.
+
+        Returns ``(updated, normalized, grad_x, grad_branch, grad_parameters)``
+        as host tensors (``out`` is filled and returned when given);
+        ``grad_parameters[0]`` is grad_weight and ``[1]`` is grad_bias.
+        """
+        if self._handle is None:
+            raise RuntimeError("the pipeline is closed")
+        tensors = (x, branch, weight, bias, grad_updated, grad_normalized)
+        if any(t.is_cuda for t in tensors):
+            raise RuntimeError("HostPipeline takes host tensors; use residual_layer_norm for device tensors")
+        if x.dtype != torch.float32 or grad_updated.dtype != torch.float32 \
+                or grad_normalized.dtype != torch.float32:
+            raise RuntimeError("x and the upstream gradients must use float32")
+        if branch.dtype != self.branch_dtype:
+            raise RuntimeError(f"branch must use {self.branch_dtype}")
+        if weight.dtype != torch.float32 or bias.dtype != torch.float32:
+            raise RuntimeError("weight and bias must use float32")
+        if x.ndim < 2 or x.shape[-1] != self.hidden:
+            raise RuntimeError(f"x must have at least two dimensions and hidden size {self.hidden}")
+        if not (branch.shape == x.shape == grad_updated.shape == grad_normalized.shape):
+            raise RuntimeError("branch and the upstream gradients must match x")
+        if tuple(weight.shape) != (self.hidden,) or tuple(bias.shape) != (self.hidden,):
+            raise RuntimeError("weight and bias must match the hidden size")
+        if not all(t.is_contiguous() for t in tensors):
+            raise RuntimeError("all tensors must be contiguous")
+        if x.numel() == 0:
+            raise RuntimeError("empty tensors are unsupported")
+        if out is None:
+            out = self.allocate_outputs(x.shape)
+        updated, normalized, grad_x, grad_branch, grad_parameters = out
+        rows = x.numel() // self.hidden
+        active = bool(training and dropout_p > 0.0)
+        with torch.cuda.device(self.device):
+            status = _load().rln_sm100_host_forward_backward(
+                self._handle,
+                x.data_ptr(), branch.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                grad_updated.data_ptr(), grad_normalized.data_ptr(),
+                updated.data_ptr(), normalized.data_ptr(), grad_x.data_ptr(),
+                grad_branch.data_ptr(), grad_parameters.data_ptr(),
+                rows, int(active), float(dropout_p), float(eps),
+                int(seed), int(offset), int(row_base), int(bool(deterministic)),
+            )
+        _check(status, "rln_sm100_host_forward_backward")
+        return out

@@ -172,6 +172,69 @@ RLN_API int rln_sm100_backward(
     int32_t deterministic,
     void* stream);
 
+/*
+ * Host-buffer pipeline: one training step (forward + backward) over rows that
+ * live in HOST memory, results returned to HOST memory.
+ *
+ * The reference has no counterpart: its entry points take device tensors only
+ * (csrc/residual_layer_norm.h:10-42) and a caller with host data pays a full
+ * copy in, a full copy out and the kernels back to back.  This entry overlaps
+ * the three: rows are cut into chunks; while chunk c is computed on the
+ * device, chunk c+1 is copied in and chunk c-1 is copied out on separate
+ * streams (both PCIe directions busy at once).  Results are identical to one
+ * rln_sm100_forward + rln_sm100_backward call over all rows: every chunk passes
+ * its global row offset to the Philox counter, and grad_weight/grad_bias are
+ * summed over chunks in chunk order.
+ *
+ * rln_sm100_host_pipeline_create ALLOCATES device staging buffers
+ * (cudaMalloc, about depth * chunk_rows * hidden * 30 bytes), streams and
+ * events on the current device; _destroy frees them.  A pipeline is bound to
+ * the device it was created on and serves one call at a time.
+ *
+ * Host pointers should be page-locked (cudaHostAlloc / cudaHostRegister /
+ * torch pin_memory); pageable memory works but the copies then do not overlap.
+ * rln_sm100_host_forward_backward returns after every output has landed in
+ * host memory (it synchronises its own streams, nothing else).
+ *
+ *   x, branch, grad_updated, grad_normalized   host in,  [rows, hidden]
+ *   weight, bias                                host in,  float32 [hidden]
+ *   updated, normalized, grad_x, grad_branch    host out, [rows, hidden]
+ *   grad_parameters                             host out, float32 [2, hidden]
+ *   other arguments as in rln_sm100_forward / rln_sm100_backward.
+ */
+typedef struct RlnHostPipeline RlnHostPipeline;
+
+RLN_API int rln_sm100_host_pipeline_create(
+    RlnHostPipeline** pipeline,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int64_t chunk_rows,
+    int32_t depth);
+
+RLN_API int rln_sm100_host_pipeline_destroy(RlnHostPipeline* pipeline);
+
+RLN_API int rln_sm100_host_forward_backward(
+    RlnHostPipeline* pipeline,
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    const float* grad_updated,
+    const float* grad_normalized,
+    float* updated,
+    float* normalized,
+    float* grad_x,
+    void* grad_branch,
+    float* grad_parameters,
+    int64_t rows,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    uint64_t seed,
+    uint64_t offset,
+    int64_t row_base,
+    int32_t deterministic);
+
 #ifdef __cplusplus
 }
 #endif
