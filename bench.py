@@ -106,7 +106,7 @@ class ClockSampler:
         0x100: "display_clock_setting",
     }
 
-    def __init__(self, device_index, interval=0.05):
+    def __init__(self, device_index, interval=0.01):
         self.device_index = device_index
         self.interval = interval
         self.samples = []
@@ -350,13 +350,14 @@ def run_native_arm(args, rank, local_rank, world):
     stop = torch.cuda.Event(enable_timing=True)
     start.record()
     for index in range(args.steps):
-        step(warmup_actual + index, not args.no_kernel_events)
+        step(warmup_actual + index, args.kernel_events_in_loop)
     stop.record()
     fence()
     timed_end = time.perf_counter()
     elapsed_ms = start.elapsed_time(stop)
-    if args.no_kernel_events:
-        for index in range(min(args.steps, 50)):
+    if not args.kernel_events_in_loop:
+        # per-kernel durations: same steps, same buffers, right after the timed region
+        for index in range(min(args.steps, 100)):
             step(warmup_actual + args.steps + index, True)
         torch.cuda.synchronize()
     forward_ms = statistics.mean(a.elapsed_time(b) for a, b in forward_events)
@@ -441,6 +442,9 @@ def run_native_arm(args, rank, local_rank, world):
                 "frac": bwd_gbs / peak,
                 "frac_of_8000": bwd_gbs / HBM_SPEC_GBS,
                 "traffic": None,
+                "timing": "CUDA events around each backward launch, "
+                          + ("inside the timed steps" if args.kernel_events_in_loop
+                             else "in a pass of the same steps right after the timed region"),
             },
             "cpu_baseline": cpu,
             "e2e": None if args.kernel_only else {
@@ -558,10 +562,11 @@ def main(argv=None):
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="h768_64Mi")
     parser.add_argument(
-        "--no-kernel-events",
+        "--kernel-events-in-loop",
         action="store_true",
-        help="do not record per-kernel CUDA events inside the timed steps "
-             "(the roofline entry is then taken from a separate pass)",
+        help="record the per-kernel CUDA events inside the K timed steps instead of in a "
+             "pass of their own right after them (an event between two kernels keeps the "
+             "second from being scheduled while the first drains, which slows the step)",
     )
     parser.add_argument(
         "--kernel-only",

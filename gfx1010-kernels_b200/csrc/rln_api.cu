@@ -274,8 +274,11 @@ extern "C" int rln_sm100_backward(
     params.deterministic = two_pass ? 1 : 0;
 
     if (parameters && !two_pass) {
-        const cudaError_t error = cudaMemsetAsync(
-            grad_parameters, 0, static_cast<size_t>(2) * hidden * sizeof(float), stream);
+        // the atomics accumulate into a zeroed buffer
+        const cudaError_t error = aligned_to(grad_parameters, 16)
+            ? rln::launch_zero(grad_parameters, 2 * hidden, stream)
+            : cudaMemsetAsync(
+                  grad_parameters, 0, static_cast<size_t>(2) * hidden * sizeof(float), stream);
         if (error != cudaSuccess) {
             return cuda_failed(error);
         }

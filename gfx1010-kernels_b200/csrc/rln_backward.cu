@@ -17,10 +17,13 @@ template <int H, typename BranchT, bool kDropout, bool kParams, bool kAligned>
 cudaError_t launch_backward_typed(const BackwardParams& params, int grid, cudaStream_t stream) {
     constexpr int kWarps = BackwardTune<H>::kWarps;
     constexpr int kRows = BackwardTune<H>::kRows;
-    rln_backward_kernel<H, BranchT, kDropout, kParams, kAligned, kWarps, kRows,
-                        BackwardTune<H>::kCtasPerSm>
-        <<<static_cast<unsigned>(grid), kWarps * kWarpSize, 0, stream>>>(params);
-    return cudaGetLastError();
+    return launch_dependent(
+        rln_backward_kernel<H, BranchT, kDropout, kParams, kAligned, kWarps, kRows,
+                            BackwardTune<H>::kCtasPerSm>,
+        static_cast<unsigned>(grid),
+        kWarps * kWarpSize,
+        stream,
+        params);
 }
 
 template <int H, bool kAligned>
@@ -101,9 +104,28 @@ cudaError_t launch_reduce_partials(
     cudaStream_t stream) {
     constexpr int kSegments = 8;
     const int blocks = (columns + kWarpSize - 1) / kWarpSize;
-    rln_reduce_partials_kernel<kSegments>
-        <<<blocks, kSegments * kWarpSize, 0, stream>>>(partials, out, partial_count, columns);
-    return cudaGetLastError();
+    return launch_dependent(
+        rln_reduce_partials_kernel<kSegments>,
+        static_cast<unsigned>(blocks),
+        kSegments * kWarpSize,
+        stream,
+        partials,
+        out,
+        partial_count,
+        columns);
+}
+
+cudaError_t launch_zero(float* out, int count, cudaStream_t stream) {
+    constexpr int kThreads = 256;
+    const int count4 = count / 4;
+    const int blocks = (count4 + kThreads - 1) / kThreads;
+    return launch_dependent(
+        rln_zero_kernel<kThreads>,
+        static_cast<unsigned>(blocks),
+        kThreads,
+        stream,
+        reinterpret_cast<float4*>(out),
+        count4);
 }
 
 }  // namespace rln

@@ -18,9 +18,12 @@ cudaError_t launch_forward_typed(const ForwardParams& params, int sm_count, cuda
     if (blocks > 0x7fffffff) {
         blocks = 0x7fffffff;  // the kernel grid-strides over the remainder
     }
-    rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows, kMinCtas>
-        <<<static_cast<unsigned>(blocks), kWarps * kWarpSize, 0, stream>>>(params);
-    return cudaGetLastError();
+    return launch_dependent(
+        rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows, kMinCtas>,
+        static_cast<unsigned>(blocks),
+        kWarps * kWarpSize,
+        stream,
+        params);
 }
 
 template <int H>

@@ -44,6 +44,31 @@ struct BackwardTune {
         H <= 128 ? 5 : (H <= 256 ? 6 : (H <= 384 ? 2 : (H <= 512 ? 3 : 2)));
 };
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may
+// be scheduled while its predecessor in the stream drains.  Every kernel of
+// this library executes griddepcontrol.wait before its first memory access, so
+// this is safe after any predecessor; it removes the launch gap between the
+// forward, the zeroing kernel and the backward of one training step.
+template <typename... KernelArgs, typename... Args>
+cudaError_t launch_dependent(
+    void (*kernel)(KernelArgs...),
+    unsigned grid,
+    unsigned block,
+    cudaStream_t stream,
+    Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(block);
+    config.dynamicSmemBytes = 0;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, args...);
+}
+
 // Remembers a failing CUDA call for rln_sm100_last_cuda_error (per thread) and
 // returns RLN_ERR_CUDA.
 int record_cuda_error(cudaError_t error);
@@ -70,6 +95,10 @@ cudaError_t launch_backward(
     const BackwardParams& params,
     int grid,
     cudaStream_t stream);
+
+// Zeroes `count` floats (count % 4 == 0, 16-byte aligned) with a kernel instead
+// of a memset node, which keeps the step's launches kernel -> kernel.
+cudaError_t launch_zero(float* out, int count, cudaStream_t stream);
 
 cudaError_t launch_reduce_partials(
     const float* partials,
