@@ -38,7 +38,13 @@ OBJECTS = ROOT / "build"
 KERNEL_LIBRARY = PACKAGE / "librln_sm100.so"
 EXTENSION = PACKAGE / "_C.so"
 
-CUDA_SOURCES = ("rln_api.cu", "rln_forward.cu", "rln_backward.cu", "rln_host_pipeline.cu")
+CUDA_SOURCES = (
+    "rln_api.cu",
+    "rln_forward.cu",
+    "rln_backward.cu",
+    "rln_host_pipeline.cu",
+    "rln_backward_static.cu",
+)
 CUDA_HEADERS = ("rln_kernels.cuh", "rln_launch.h")
 NVCC_FLAGS = (
     "-gencode",

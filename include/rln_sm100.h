@@ -173,6 +173,59 @@ RLN_API int rln_sm100_backward(
     void* stream);
 
 /*
+ * Backward for callers that must not allocate: same outputs as
+ * rln_sm100_backward(..., deterministic = 1) with parameter gradients, but the
+ * per-CTA partials are kept in a scratch array built into this library's
+ * device image, so no workspace is passed and nothing is allocated -- not by
+ * this call and not by anything it calls.
+ *
+ * It has no counterpart in the reference, whose backward always allocates its
+ * partial tensor through torch.  It exists for hosts that cannot do that:
+ * runtimes that gave all device memory to their own pool and forbid allocation
+ * calls inside an operator, plugin interfaces whose run step may not allocate,
+ * and loops where the device-wide synchronisation of a cudaMalloc or cudaFree
+ * is not acceptable.  The caller still provides every input and output buffer.
+ *
+ * Limits and rules:
+ *   - The scratch is RLN_STATIC_SCRATCH_BYTES (4 MiB) per GPU, held by every
+ *     GPU that loads the library until the process exits.  A call needs
+ *     grid * 2 * hidden * 4 bytes (grid = the persistent backward grid, at
+ *     most 6 CTAs per SM): at most 2.4 MB on a 148-SM B200 for every supported
+ *     width and any row count.  A device on which a call would need more gets
+ *     RLN_ERR_LIMIT ("size exceeds a fixed maximum of this entry point").
+ *   - The first call on each device looks the scratch address up (one
+ *     cudaGetSymbolAddress with that device current, then cached).  Make that
+ *     first call during set-up, before any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the
+ *     last call left there.  Nothing in it needs clearing (each call overwrites
+ *     every partial it later reads), but two calls that overlap on the GPU --
+ *     different streams, or different host threads -- race on it and give
+ *     wrong grad_parameters.  Serialise calls per device.
+ *   - grad_parameters is required (this is the variant that reduces them).
+ *
+ * Arguments as in rln_sm100_backward.
+ */
+#define RLN_STATIC_SCRATCH_BYTES (4u << 20)
+
+RLN_API int rln_sm100_backward_static_scratch(
+    const float* grad_updated,
+    const float* grad_normalized,
+    const float* updated,
+    const float* weight,
+    const float* mean,
+    const float* rstd,
+    const uint32_t* dropout_mask,
+    float* grad_x,
+    void* grad_branch,
+    float* grad_parameters,
+    int64_t rows,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int32_t dropout_active,
+    float dropout_p,
+    void* stream);
+
+/*
  * Host-buffer pipeline: one training step (forward + backward) over rows that
  * live in HOST memory, results returned to HOST memory.
  *
