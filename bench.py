@@ -462,7 +462,7 @@ def run_native_arm(args, rank, local_rank, world):
                                    "implementation='gfx1010') + torch.autograd.grad, results "
                                    "copied to pinned host, one stream",
             },
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": 3 * args.steps,  # forward, zeroing kernel, backward
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
