@@ -53,6 +53,9 @@ WORKLOADS = {
     "c3_h1024": (32768, 1024, torch.float16, 0.1),
     "c5_64x4096x1024": (262144, 1024, torch.float16, 0.1),
 }
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch from
+# the ncu capture summarised in profiles/rln_backward_kernel_h768_64Mi.md, per workload.
+NCU_BACKWARD_TRAFFIC_BYTES = {"h768_64Mi": 814_416_128 + 351_629_824}
 CPU_SAMPLE_ROWS = 8192
 EPS = 1e-5
 
@@ -441,7 +444,9 @@ def run_native_arm(args, rank, local_rank, world):
                 "unit": "GB/s",
                 "frac": bwd_gbs / peak,
                 "frac_of_8000": bwd_gbs / HBM_SPEC_GBS,
-                "traffic": None,
+                "traffic": NCU_BACKWARD_TRAFFIC_BYTES.get(args.workload),
+                "traffic_unit": "bytes per launch (ncu dram read + write)",
+                "algorithmic_bytes_per_launch": bwd_bytes,
                 "timing": "CUDA events around each backward launch, "
                           + ("inside the timed steps" if args.kernel_events_in_loop
                              else "in a pass of the same steps right after the timed region"),

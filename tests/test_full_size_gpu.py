@@ -96,7 +96,15 @@ def test_full_size_forward_and_backward_properties(name):
     for a, b in zip(once[1:], twice[1:]):
         assert torch.equal(a, b)                      # deterministic replay
     for a, b in zip(once[1:], doubled[1:]):
-        assert torch.equal((2 * a.float()).to(a.dtype), b)   # linearity, exact
+        expected = 2 * a.float()
+        if a.dtype == torch.float16:
+            # doubling commutes with rounding except among fp16 subnormals,
+            # where the grid spacing (2**-24) does not scale with the value
+            normal = a.float().abs() >= 2.0 ** -13
+            assert torch.equal(expected[normal], b.float()[normal])
+            assert (expected - b.float()).abs().max().item() <= 2.0 ** -23
+        else:
+            assert torch.equal(expected, b)               # linearity, exact
     assert torch.equal(once[1], atomic[1]) and torch.equal(once[2], atomic[2])
 
     grad_x, grad_branch, grad_parameters = once[1], once[2], once[3]
