@@ -302,8 +302,6 @@ def run_native_arm(args, rank, local_rank, world):
     forward_events, backward_events = [], []
 
     def step(index, record):
-        if flush is not None:
-            flush.zero_()
         if record:
             e0 = torch.cuda.Event(enable_timing=True)
             e1 = torch.cuda.Event(enable_timing=True)
@@ -341,6 +339,8 @@ def run_native_arm(args, rank, local_rank, world):
     done = 0
     settle = 0.0 if args.kernel_only else 1.0
     while done < max(args.warmup, 3) or (time.perf_counter() - warm_begin < settle and done < 5000):
+        if flush is not None:
+            flush.zero_()
         step(done, False)
         done += 1
         if done % 50 == 0:
@@ -351,16 +351,30 @@ def run_native_arm(args, rank, local_rank, world):
     timed_begin = time.perf_counter()
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
+    step_events = []
     start.record()
     for index in range(args.steps):
+        if flush is not None:
+            # the L2 flush is not part of a step: bracket every step on its own
+            flush.zero_()
+            begin_event = torch.cuda.Event(enable_timing=True)
+            end_event = torch.cuda.Event(enable_timing=True)
+            begin_event.record()
         step(warmup_actual + index, args.kernel_events_in_loop)
+        if flush is not None:
+            end_event.record()
+            step_events.append((begin_event, end_event))
     stop.record()
     fence()
     timed_end = time.perf_counter()
     elapsed_ms = start.elapsed_time(stop)
+    if step_events:
+        elapsed_ms = sum(a.elapsed_time(b) for a, b in step_events)
     if not args.kernel_events_in_loop:
         # per-kernel durations: same steps, same buffers, right after the timed region
         for index in range(min(args.steps, 100)):
+            if flush is not None:
+                flush.zero_()
             step(warmup_actual + args.steps + index, True)
         torch.cuda.synchronize()
     forward_ms = statistics.mean(a.elapsed_time(b) for a, b in forward_events)
