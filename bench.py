@@ -22,6 +22,7 @@ torch decomposition (the reference's CPU path) timed on this machine's cores.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -283,7 +284,11 @@ def run_native_arm(args, rank, local_rank, world):
     if not status.available:
         raise RuntimeError(f"native backend unavailable: {status.reason}")
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # a short timeout: a rank that stops calling collectives must surface as an
+        # error within minutes, not hold the GPUs for the default ten
+        dist.init_process_group(
+            "nccl", device_id=device, timeout=datetime.timedelta(seconds=120)
+        )
 
     rows, hidden, branch_dtype, dropout_p = WORKLOADS[args.workload]
     branch_bytes = 2 if branch_dtype == torch.float16 else 4
@@ -334,18 +339,34 @@ def run_native_arm(args, rank, local_rank, world):
     sampler = ClockSampler(local_rank)
     sampler.start()
 
-    # warm-up: at least W steps and long enough for the clock sampler to see load
+    # warm-up: W steps, then as many more as bring the loaded span to about a second
+    # (clock settling + clock samples).  The count is agreed between the ranks --
+    # every step contains a collective, so all ranks must run the same number.
+    def warm(count, first):
+        for index in range(count):
+            if flush is not None:
+                flush.zero_()
+            step(first + index, False)
+            if index % 50 == 49:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+
     warm_begin = time.perf_counter()
-    done = 0
-    settle = 0.0 if args.kernel_only else 1.0
-    while done < max(args.warmup, 3) or (time.perf_counter() - warm_begin < settle and done < 5000):
-        if flush is not None:
-            flush.zero_()
-        step(done, False)
-        done += 1
-        if done % 50 == 0:
-            torch.cuda.synchronize()
-    warmup_actual = done
+    base = max(args.warmup, 3)
+    warm(base, 0)
+    warmup_actual = base
+    if not args.kernel_only:
+        probe_begin = time.perf_counter()
+        warm(10, base)          # timed probe (the first steps above carry one-time set-up)
+        warmup_actual += 10
+        per_step = (time.perf_counter() - probe_begin) / 10
+        extra = int(min(5000, 1.0 / max(per_step, 1e-6)))
+        if world > 1:
+            agreed = torch.tensor([extra], device=device, dtype=torch.int64)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+            extra = int(agreed.item())
+        warm(extra, warmup_actual)
+        warmup_actual += extra
 
     fence()
     timed_begin = time.perf_counter()
