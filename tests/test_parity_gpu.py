@@ -366,3 +366,46 @@ def test_c_abi_rejects_bad_arguments_on_device():
         None, 0, 4, 128, 1, 0, 0.0, 1, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
     )
     assert status == -7
+
+
+@pytest.mark.parametrize("hidden,branch_dtype", [(128, torch.float32), (768, torch.float16),
+                                                 (1024, torch.float16)])
+def test_cuda_path_matches_the_scalar_c_oracle(hidden, branch_dtype):
+    """Independent second oracle: ``oracle/rln_oracle.c`` walks the reference
+    kernels' formulas one element at a time."""
+    from oracle import c_oracle
+
+    rows, p, eps, seed, offset, row_base = 29, 0.15, 1e-5, 21, 4, 1 << 33
+    x, branch, weight, bias, grad_updated, grad_normalized = draw_inputs(
+        (rows,), hidden, branch_dtype, 31
+    )
+    half = branch_dtype == torch.float16
+    status, updated, normalized, mean, rstd, mask = cabi.forward(
+        x, branch, weight, bias, p, eps, True, seed=seed, offset=offset, row_base=row_base
+    )
+    assert status == 0
+    keep, words = c_oracle.keep_mask(rows, hidden, p, seed, offset, row_base)
+    assert np.array_equal(mask.cpu().numpy(), words)
+    expected = c_oracle.forward(
+        x.cpu().numpy(), branch.float().cpu().numpy(), weight.cpu().numpy(), bias.cpu().numpy(),
+        keep, p, eps, half,
+    )
+    assert np.array_equal(updated.cpu().numpy(), expected[0])
+    np.testing.assert_allclose(normalized.cpu().numpy(), expected[1], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(mean.cpu().numpy(), expected[2], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(rstd.cpu().numpy(), expected[3], rtol=1e-5, atol=0)
+    status, grad_x, grad_branch, grad_parameters = cabi.backward(
+        grad_updated, grad_normalized, updated, weight, mean, rstd, mask, p, True,
+        branch_dtype, True,
+    )
+    assert status == 0
+    reference = c_oracle.backward(
+        grad_updated.cpu().numpy(), grad_normalized.cpu().numpy(), updated.cpu().numpy(),
+        weight.cpu().numpy(), mean.cpu().numpy(), rstd.cpu().numpy(), keep, p, half,
+    )
+    np.testing.assert_allclose(grad_x.cpu().numpy(), reference[0], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(
+        grad_branch.float().cpu().numpy(), reference[1], rtol=2e-3 if half else 1e-5, atol=1e-5
+    )
+    np.testing.assert_allclose(grad_parameters[0].cpu().numpy(), reference[2], rtol=1e-4, atol=5e-5)
+    np.testing.assert_allclose(grad_parameters[1].cpu().numpy(), reference[3], rtol=1e-4, atol=5e-5)
