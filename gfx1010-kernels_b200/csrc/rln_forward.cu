@@ -8,22 +8,33 @@ template <int H, typename BranchT, bool kDropout, bool kAligned>
 cudaError_t launch_forward_typed(const ForwardParams& params, int sm_count, cudaStream_t stream) {
     constexpr int kWarps = ForwardTune<H>::kWarps;
     constexpr int kRows = ForwardTune<H>::kRows;
+    constexpr int kLanes = ForwardTune<H>::kLanes;
     constexpr int kMinCtas = ForwardTune<H>::kMinCtas;
-    constexpr int64_t kRowsPerCta = static_cast<int64_t>(kWarps) * kRows;
+    constexpr int64_t kRowsPerCta =
+        static_cast<int64_t>(kWarps) * (kLanes == kWarpSize ? kRows : kWarpSize / kLanes);
     int64_t blocks = (params.rows + kRowsPerCta - 1) / kRowsPerCta;
     if (ForwardTune<H>::kPersistent) {
         const int64_t resident = static_cast<int64_t>(sm_count) * kMinCtas;
         blocks = blocks < resident ? blocks : resident;
     }
     if (blocks > 0x7fffffff) {
-        blocks = 0x7fffffff;  // the kernel grid-strides over the remainder
+        blocks = 0x7fffffff;  // the kernels grid-stride over the remainder
     }
-    return launch_dependent(
-        rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows, kMinCtas>,
-        static_cast<unsigned>(blocks),
-        kWarps * kWarpSize,
-        stream,
-        params);
+    if constexpr (kLanes == kWarpSize) {
+        return launch_dependent(
+            rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows, kMinCtas>,
+            static_cast<unsigned>(blocks),
+            kWarps * kWarpSize,
+            stream,
+            params);
+    } else {
+        return launch_dependent(
+            rln_forward_subwarp_kernel<H, BranchT, kDropout, kAligned, kWarps, kLanes, kMinCtas>,
+            static_cast<unsigned>(blocks),
+            kWarps * kWarpSize,
+            stream,
+            params);
+    }
 }
 
 template <int H>

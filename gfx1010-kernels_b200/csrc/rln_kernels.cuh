@@ -437,6 +437,152 @@ rln_forward_kernel(const ForwardParams p) {
 }
 
 // ---------------------------------------------------------------------------
+// Forward for narrow rows.  A group of kLanes (8 or 16) lanes owns one row, so
+// a warp works on 32/kLanes rows at once: the shuffle butterflies shrink to
+// log2(kLanes) steps and every shuffle, compare and store instruction serves
+// several rows.  Same arithmetic per element, same lane-group mask packing
+// (8 lanes -> one word), so results are bit-identical to the one-warp-per-row
+// kernel.  Row validity is per lane group here (not warp-uniform): loads and
+// stores are predicated, shuffles are executed by the whole warp.
+// ---------------------------------------------------------------------------
+template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kLanes,
+          int kMinCtas = 1>
+__global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
+rln_forward_subwarp_kernel(const ForwardParams p) {
+    static_assert(kLanes == 8 || kLanes == 16, "a row is owned by 8 or 16 lanes");
+    static_assert(H % (4 * kLanes) == 0, "hidden must be a multiple of 4 * kLanes");
+    constexpr int V = H / (4 * kLanes);  // float4 chunks per lane
+    constexpr int kRowsPerWarp = kWarpSize / kLanes;
+    constexpr int kChunksPerRow = H / 4;
+    constexpr int kWordsPerRow = H / 32;
+    constexpr float kInvH = 1.0f / static_cast<float>(H);
+    using IO = BranchIO<BranchT>;
+
+    const int lane = threadIdx.x & (kWarpSize - 1);
+    const int warp = threadIdx.x / kWarpSize;
+    const int lane_in_row = lane & (kLanes - 1);
+    const int row_in_warp = lane / kLanes;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRowsPerWarp;
+    grid_dependency_sync();
+
+    for (int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRowsPerWarp;
+         first < p.rows; first += stride) {
+        const int64_t row = first + row_in_warp;
+        const bool valid = row < p.rows;
+        float4 u[V];
+        float4 b[V];
+        uint32_t nibble[V];
+
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            u[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            b[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            nibble[k] = 0u;
+            if (valid) {
+                const int64_t chunk = row * kChunksPerRow + lane_in_row + k * kLanes;
+                u[k] = load_f4<kAligned>(p.x, chunk);
+                b[k] = IO::template load<kAligned>(p.branch, chunk);
+            }
+        }
+        if constexpr (kDropout) {
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                const uint64_t group =
+                    static_cast<uint64_t>(p.row_base + row) * kChunksPerRow
+                    + static_cast<uint64_t>(lane_in_row + k * kLanes);
+                const uint4 random = philox4x32_10(
+                    make_uint4(
+                        p.offset_lo,
+                        p.offset_hi,
+                        static_cast<uint32_t>(group),
+                        static_cast<uint32_t>(group >> 32)),
+                    p.seed_lo,
+                    p.seed_hi);
+                nibble[k] =
+                    (random.x >= p.threshold ? 1u : 0u)
+                    | (random.y >= p.threshold ? 2u : 0u)
+                    | (random.z >= p.threshold ? 4u : 0u)
+                    | (random.w >= p.threshold ? 8u : 0u);
+            }
+        }
+
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            float4 dropped = b[k];
+            if constexpr (kDropout) {
+                const uint32_t n = nibble[k];
+                dropped.x = drop_one<BranchT>(dropped.x, n & 1u, p.scale);
+                dropped.y = drop_one<BranchT>(dropped.y, n & 2u, p.scale);
+                dropped.z = drop_one<BranchT>(dropped.z, n & 4u, p.scale);
+                dropped.w = drop_one<BranchT>(dropped.w, n & 8u, p.scale);
+            }
+            float4 value = u[k];
+            value.x = __fadd_rn(value.x, dropped.x);
+            value.y = __fadd_rn(value.y, dropped.y);
+            value.z = __fadd_rn(value.z, dropped.z);
+            value.w = __fadd_rn(value.w, dropped.w);
+            u[k] = value;
+            if (valid) {
+                store_f4<kAligned>(
+                    p.updated, row * kChunksPerRow + lane_in_row + k * kLanes, value);
+            }
+            sum += (value.x + value.y) + (value.z + value.w);
+        }
+#pragma unroll
+        for (int delta = kLanes / 2; delta > 0; delta >>= 1) {
+            sum += __shfl_xor_sync(kFullMask, sum, delta);
+        }
+        const float row_mean = sum * kInvH;
+        float square_sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            const float cx = u[k].x - row_mean;
+            const float cy = u[k].y - row_mean;
+            const float cz = u[k].z - row_mean;
+            const float cw = u[k].w - row_mean;
+            square_sum += (cx * cx + cy * cy) + (cz * cz + cw * cw);
+        }
+#pragma unroll
+        for (int delta = kLanes / 2; delta > 0; delta >>= 1) {
+            square_sum += __shfl_xor_sync(kFullMask, square_sum, delta);
+        }
+        const float row_rstd = rsqrtf(square_sum * kInvH + p.eps);
+        if (valid && lane_in_row == 0) {
+            p.mean[row] = row_mean;
+            p.rstd[row] = row_rstd;
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+            const int pchunk = lane_in_row + k * kLanes;
+            const float4 gamma = load_param<kAligned>(p.weight, pchunk);
+            const float4 beta = load_param<kAligned>(p.bias, pchunk);
+            float4 out;
+            out.x = (u[k].x - row_mean) * row_rstd * gamma.x + beta.x;
+            out.y = (u[k].y - row_mean) * row_rstd * gamma.y + beta.y;
+            out.z = (u[k].z - row_mean) * row_rstd * gamma.z + beta.z;
+            out.w = (u[k].w - row_mean) * row_rstd * gamma.w + beta.w;
+            if (valid) {
+                store_f4<kAligned>(p.normalized, row * kChunksPerRow + pchunk, out);
+            }
+        }
+        if constexpr (kDropout) {
+            // chunk c = lane_in_row + kLanes*k -> nibble (c & 7) of word c / 8
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                uint32_t word = nibble[k] << (4 * (lane & 7));
+                word |= __shfl_xor_sync(kFullMask, word, 1);
+                word |= __shfl_xor_sync(kFullMask, word, 2);
+                word |= __shfl_xor_sync(kFullMask, word, 4);
+                if (valid && (lane & 7) == 0) {
+                    p.mask[row * kWordsPerRow + (lane_in_row + k * kLanes) / 8] = word;
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Backward.  Persistent grid; each warp walks groups of kRows consecutive rows
 // with a fixed stride, so the set and order of rows a warp (and a CTA) sums is
 // a pure function of (rows, gridDim) -- the basis of the bitwise-replay mode.

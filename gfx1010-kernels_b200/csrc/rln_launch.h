@@ -19,16 +19,20 @@ namespace rln {
 //             forward: fewer warps leave HBM latency exposed, more warps cut
 //             the registers a warp can keep in flight;
 //   kPersistent (forward) launch exactly sm_count * kMinCtas CTAs that
-//             grid-stride, instead of one CTA per kWarps * kRows rows.  Only
-//             pays for the narrowest rows, where a CTA would otherwise live
-//             for a single 512-byte row per warp.
+//             grid-stride, instead of one CTA per kWarps * kRows rows.  Not
+//             used by the current table: with several rows per warp even the
+//             narrowest rows are fastest with one short-lived CTA per row group.
 template <int H>
 struct ForwardTune {
-    static constexpr int kWarps = H <= 128 ? 8 : 4;
+    // kLanes lanes own one row: 32 = one warp per row (rln_forward_kernel);
+    // 8 / 16 = several rows per warp (rln_forward_subwarp_kernel), which wins
+    // for the two narrowest widths (H=128: +14 %, H=256: +1 %) and loses from
+    // H=384 up.
+    static constexpr int kLanes = H <= 128 ? 8 : (H <= 256 ? 16 : 32);
+    static constexpr int kWarps = 4;
     static constexpr int kRows = 1;
-    static constexpr int kMinCtas =
-        H <= 128 ? 6 : (H <= 384 ? 8 : (H <= 512 ? 6 : 4));
-    static constexpr bool kPersistent = H <= 128;
+    static constexpr int kMinCtas = H <= 256 ? 6 : (H <= 384 ? 8 : (H <= 512 ? 6 : 4));
+    static constexpr bool kPersistent = false;
 };
 
 // The backward grid is persistent (register-resident parameter-gradient
