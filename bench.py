@@ -265,8 +265,8 @@ def workload_config(name, gpus):
         "training": True,
         "parameter_gradients": "atomic (non-deterministic mode)",
         "parallelism": f"rows sharded over {gpus} GPU(s); NCCL all-reduce of the [2,H] grads, "
-                       "asynchronous (overlaps the next step's forward, waited for inside "
-                       "the timed region)" if gpus > 1
+                       "asynchronous (overlaps the next step's forward, waited for before "
+                       "that step's backward, inside the timed region)" if gpus > 1
         else "1 GPU",
         "l2": "inputs larger than L2 (no flush needed)" if rows * hidden * 4 > 126e6
         else "flushed between steps",
@@ -323,6 +323,11 @@ def run_native_arm(args, rank, local_rank, world):
         updated, normalized, mean, rstd, mask = _C.residual_layer_norm_forward_seeded(
             x, branch, weight, bias, dropout_p, EPS, True, 128, seed, 4 * index, row_base
         )
+        # The backward is a persistent grid that fills every SM exactly once; a
+        # communication kernel still resident from the previous step would push
+        # part of it into a second wave.  So the previous all-reduce may overlap
+        # the forward (dynamically scheduled CTAs) but must be done before this.
+        finish_pending()
         if record:
             e1.record()
         gradients = _C.residual_layer_norm_backward(
@@ -337,8 +342,7 @@ def run_native_arm(args, rank, local_rank, world):
             # grad_weight and grad_bias are views of one [2, H] buffer.  The all-reduce
             # is asynchronous: it runs on NCCL's stream under the NEXT step's forward
             # (which does not depend on it) and is waited for before that step's
-            # all-reduce is issued, and once more before the timed region ends.
-            finish_pending()
+            # backward is launched, and once more before the timed region ends.
             buffer = gradients[2]._base if gradients[2]._base is not None else gradients[2]
             pending.append((dist.all_reduce(buffer, async_op=True), buffer))
         return normalized, gradients
