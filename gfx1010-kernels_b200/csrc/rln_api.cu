@@ -87,7 +87,9 @@ extern "C" const char* rln_sm100_status_string(int status) {
 
 extern "C" int rln_sm100_last_cuda_error(void) { return tls_last_cuda_error; }
 
-extern "C" int rln_sm100_forward(
+namespace {
+
+int forward_launch(
     const float* x,
     const void* branch,
     const float* weight,
@@ -105,6 +107,8 @@ extern "C" int rln_sm100_forward(
     float eps,
     uint64_t seed,
     uint64_t offset,
+    const int64_t* device_seed,
+    const int64_t* device_offset,
     int64_t row_base,
     void* stream) {
     if (!supported_hidden(hidden)) {
@@ -154,6 +158,9 @@ extern "C" int rln_sm100_forward(
     params.seed_hi = static_cast<uint32_t>(seed >> 32);
     params.offset_lo = static_cast<uint32_t>(offset);
     params.offset_hi = static_cast<uint32_t>(offset >> 32);
+    params.device_seed = device_seed;
+    params.device_offset = device_offset;
+    params.device_offset_extra = device_seed != nullptr ? offset : 0;
 
     int sm_count = 0;
     const int status = current_sm_count(&sm_count);
@@ -169,6 +176,69 @@ extern "C" int rln_sm100_forward(
         sm_count,
         static_cast<cudaStream_t>(stream));
     return error == cudaSuccess ? RLN_OK : cuda_failed(error);
+}
+
+}  // namespace
+
+extern "C" int rln_sm100_forward(
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    float* updated,
+    float* normalized,
+    float* mean,
+    float* rstd,
+    uint32_t* dropout_mask,
+    int64_t rows,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    uint64_t seed,
+    uint64_t offset,
+    int64_t row_base,
+    void* stream) {
+    return forward_launch(
+        x, branch, weight, bias, updated, normalized, mean, rstd, dropout_mask, rows, hidden,
+        branch_is_half, dropout_active, dropout_p, eps, seed, offset, nullptr, nullptr, row_base,
+        stream);
+}
+
+extern "C" int rln_sm100_forward_device_rng(
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    float* updated,
+    float* normalized,
+    float* mean,
+    float* rstd,
+    uint32_t* dropout_mask,
+    int64_t rows,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    const int64_t* device_seed,
+    const int64_t* device_offset,
+    uint64_t offset_extra,
+    int64_t row_base,
+    void* stream) {
+    if (dropout_active && (device_seed == nullptr || device_offset == nullptr)) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    if (dropout_active
+        && (!aligned_to(device_seed, 8) || !aligned_to(device_offset, 8))) {
+        return RLN_ERR_ALIGNMENT;
+    }
+    return forward_launch(
+        x, branch, weight, bias, updated, normalized, mean, rstd, dropout_mask, rows, hidden,
+        branch_is_half, dropout_active, dropout_p, eps, 0, offset_extra,
+        dropout_active ? device_seed : nullptr, dropout_active ? device_offset : nullptr,
+        row_base, stream);
 }
 
 extern "C" int64_t rln_sm100_backward_workspace_bytes(

@@ -25,6 +25,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 
+#include <atomic>
 #include <cstdint>
 #include <mutex>
 #include <tuple>
@@ -176,6 +177,68 @@ void check_backward_inputs(
 
 }  // namespace
 
+namespace {
+
+std::atomic<bool> graph_capture_allowed{false};
+
+// Validation, allocation and launch shared by the three forward entries.  The
+// Philox state is either immediate (device_seed == nullptr) or behind device
+// pointers (a launch that is being recorded into a CUDA graph).
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> forward_launch(
+    const at::Tensor& x,
+    const at::Tensor& branch,
+    const at::Tensor& weight,
+    const at::Tensor& bias,
+    double dropout_p,
+    double eps,
+    bool training,
+    int64_t threads,
+    uint64_t seed,
+    uint64_t offset,
+    const int64_t* device_seed,
+    const int64_t* device_offset,
+    int64_t row_base) {
+    check_forward_inputs(x, branch, weight, bias, dropout_p, eps, threads);
+    TORCH_CHECK(row_base >= 0, "row_base must be non-negative");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int64_t hidden = x.size(-1);
+    const int64_t row_count = x.numel() / hidden;
+    auto updated = at::empty_like(x);
+    auto normalized = at::empty_like(x);
+    auto mean = at::empty({row_count}, x.options());
+    auto rstd = at::empty({row_count}, x.options());
+    const bool dropout = training && dropout_p > 0.0;
+    auto dropout_mask = at::empty(
+        {dropout ? row_count * (hidden / kMaskColumnsPerWord) : 0},
+        x.options().dtype(at::kInt));
+    const auto stream = c10::cuda::getCurrentCUDAStream(x.device().index()).stream();
+    uint32_t* mask_pointer =
+        dropout ? reinterpret_cast<uint32_t*>(dropout_mask.data_ptr<int32_t>()) : nullptr;
+    const int32_t branch_is_half = branch.scalar_type() == at::kHalf ? 1 : 0;
+    int status = RLN_OK;
+    if (device_seed != nullptr) {
+        status = rln_sm100_forward_device_rng(
+            x.data_ptr<float>(), branch.data_ptr(), weight.data_ptr<float>(),
+            bias.data_ptr<float>(), updated.data_ptr<float>(), normalized.data_ptr<float>(),
+            mean.data_ptr<float>(), rstd.data_ptr<float>(), mask_pointer, row_count,
+            static_cast<int32_t>(hidden), branch_is_half, dropout ? 1 : 0,
+            static_cast<float>(dropout_p), static_cast<float>(eps), device_seed, device_offset,
+            offset, row_base, stream);
+    } else {
+        status = rln_sm100_forward(
+            x.data_ptr<float>(), branch.data_ptr(), weight.data_ptr<float>(),
+            bias.data_ptr<float>(), updated.data_ptr<float>(), normalized.data_ptr<float>(),
+            mean.data_ptr<float>(), rstd.data_ptr<float>(), mask_pointer, row_count,
+            static_cast<int32_t>(hidden), branch_is_half, dropout ? 1 : 0,
+            static_cast<float>(dropout_p), static_cast<float>(eps), seed, offset, row_base,
+            stream);
+    }
+    check_status(status, "residual_layer_norm_forward");
+    return {updated, normalized, mean, rstd, dropout_mask};
+}
+
+}  // namespace
+
 // Forward with an explicit Philox (seed, offset) and a global row offset: the
 // entry a row-sharded caller uses so that every shard reproduces the mask of
 // the unsharded call.  Consumes no generator state.
@@ -192,50 +255,19 @@ residual_layer_norm_forward_seeded(
     int64_t seed,
     int64_t offset,
     int64_t row_base) {
-    check_forward_inputs(x, branch, weight, bias, dropout_p, eps, threads);
-    TORCH_CHECK(row_base >= 0, "row_base must be non-negative");
-    c10::cuda::CUDAGuard guard(x.device());
-    const int64_t hidden = x.size(-1);
-    const int64_t row_count = x.numel() / hidden;
-    auto updated = at::empty_like(x);
-    auto normalized = at::empty_like(x);
-    auto mean = at::empty({row_count}, x.options());
-    auto rstd = at::empty({row_count}, x.options());
-    const bool dropout = training && dropout_p > 0.0;
-    auto dropout_mask = at::empty(
-        {dropout ? row_count * (hidden / kMaskColumnsPerWord) : 0},
-        x.options().dtype(at::kInt));
-    const auto stream = c10::cuda::getCurrentCUDAStream(x.device().index()).stream();
-    const int status = rln_sm100_forward(
-        x.data_ptr<float>(),
-        branch.data_ptr(),
-        weight.data_ptr<float>(),
-        bias.data_ptr<float>(),
-        updated.data_ptr<float>(),
-        normalized.data_ptr<float>(),
-        mean.data_ptr<float>(),
-        rstd.data_ptr<float>(),
-        dropout ? reinterpret_cast<uint32_t*>(dropout_mask.data_ptr<int32_t>()) : nullptr,
-        row_count,
-        static_cast<int32_t>(hidden),
-        branch.scalar_type() == at::kHalf ? 1 : 0,
-        dropout ? 1 : 0,
-        static_cast<float>(dropout_p),
-        static_cast<float>(eps),
-        static_cast<uint64_t>(seed),
-        static_cast<uint64_t>(offset),
-        row_base,
-        stream);
-    check_status(status, "residual_layer_norm_forward");
-    return {updated, normalized, mean, rstd, dropout_mask};
+    return forward_launch(
+        x, branch, weight, bias, dropout_p, eps, training, threads,
+        static_cast<uint64_t>(seed), static_cast<uint64_t>(offset), nullptr, nullptr, row_base);
 }
 
 // Counterpart of residual_layer_norm_forward_hip
 // (csrc/residual_layer_norm_kernel.hip:1720-1827): the Philox state comes from
 // the device's default torch generator, advanced under its mutex by the same
 // increment the reference uses (:1767-1774) so that the generator state after
-// the call matches the reference's; graph capture with dropout is refused
-// (:1758-1777); eval mode and p == 0 consume no generator state.
+// the call matches the reference's; eval mode and p == 0 consume no generator
+// state.  Graph capture with dropout is refused as in the reference
+// (:1758-1777) unless set_graph_capture_allowed(true) was called, in which
+// case the launch takes torch's graph-safe generator state by pointer.
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor>
 residual_layer_norm_forward_cuda(
     const at::Tensor& x,
@@ -249,11 +281,14 @@ residual_layer_norm_forward_cuda(
     check_forward_inputs(x, branch, weight, bias, dropout_p, eps, threads);
     uint64_t seed = 0;
     uint64_t offset = 0;
+    const int64_t* device_seed = nullptr;
+    const int64_t* device_offset = nullptr;
     if (training && dropout_p > 0.0) {
         c10::cuda::CUDAGuard guard(x.device());
+        const bool capturing = c10::cuda::currentStreamCaptureStatusMayInitCtx()
+            != c10::cuda::CaptureStatus::None;
         TORCH_CHECK(
-            c10::cuda::currentStreamCaptureStatusMayInitCtx()
-                == c10::cuda::CaptureStatus::None,
+            !capturing || graph_capture_allowed.load(),
             "native residual LayerNorm dropout does not support HIP graph capture");
         auto* generator = at::get_generator_or_default<at::CUDAGeneratorImpl>(
             std::nullopt, at::cuda::detail::getDefaultCUDAGenerator(x.device().index()));
@@ -265,24 +300,22 @@ residual_layer_norm_forward_cuda(
             std::lock_guard<std::mutex> lock(generator->mutex_);
             state = generator->philox_cuda_state(increment);
         }
-        TORCH_CHECK(
-            !state.captured_,
-            "native residual LayerNorm dropout does not support HIP graph capture");
-        seed = state.seed_.val;
-        offset = state.offset_.val;
+        if (state.captured_) {
+            TORCH_CHECK(
+                graph_capture_allowed.load(),
+                "native residual LayerNorm dropout does not support HIP graph capture");
+            // graph-safe generator state: read on the device at replay time
+            device_seed = state.seed_.ptr;
+            device_offset = state.offset_.ptr;
+            offset = state.offset_intragraph_;
+        } else {
+            seed = state.seed_.val;
+            offset = state.offset_.val;
+        }
     }
-    return residual_layer_norm_forward_seeded(
-        x,
-        branch,
-        weight,
-        bias,
-        dropout_p,
-        eps,
-        training,
-        threads,
-        static_cast<int64_t>(seed),
-        static_cast<int64_t>(offset),
-        0);
+    return forward_launch(
+        x, branch, weight, bias, dropout_p, eps, training, threads, seed, offset, device_seed,
+        device_offset, 0);
 }
 
 // Counterpart of residual_layer_norm_backward_hip
@@ -482,4 +515,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, module) {
     module.def("residual_layer_norm_backward", &residual_layer_norm_backward_cuda);
     module.def("residual_layer_norm_forward_seeded", &residual_layer_norm_forward_seeded);
     module.def("abi_version", &rln_sm100_abi_version);
+    module.def("set_graph_capture_allowed", [](bool allowed) {
+        graph_capture_allowed.store(allowed);
+    });
+    module.def("graph_capture_allowed", []() { return graph_capture_allowed.load(); });
 }

@@ -53,6 +53,20 @@ struct ForwardParams {
     uint32_t seed_hi;
     uint32_t offset_lo;
     uint32_t offset_hi;
+    // Philox state kept on the device (set when the launch is recorded into a
+    // CUDA graph, so that each replay sees the generator's current state):
+    // seed = *device_seed, offset = *device_offset + device_offset_extra.
+    // nullptr = use the immediate values above.
+    const int64_t* device_seed;
+    const int64_t* device_offset;
+    uint64_t device_offset_extra;
+};
+
+struct PhiloxState {
+    uint32_t seed_lo;
+    uint32_t seed_hi;
+    uint32_t offset_lo;
+    uint32_t offset_hi;
 };
 
 struct BackwardParams {
@@ -115,6 +129,21 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 counter, uint32_t key0, uin
         key1 += kW1;
     }
     return counter;
+}
+
+// (seed, offset) of this launch: immediate, or read from device memory.
+__device__ __forceinline__ PhiloxState resolve_philox_state(const ForwardParams& p) {
+    PhiloxState state = {p.seed_lo, p.seed_hi, p.offset_lo, p.offset_hi};
+    if (p.device_seed != nullptr) {
+        const uint64_t seed = static_cast<uint64_t>(__ldg(p.device_seed));
+        const uint64_t offset =
+            static_cast<uint64_t>(__ldg(p.device_offset)) + p.device_offset_extra;
+        state.seed_lo = static_cast<uint32_t>(seed);
+        state.seed_hi = static_cast<uint32_t>(seed >> 32);
+        state.offset_lo = static_cast<uint32_t>(offset);
+        state.offset_hi = static_cast<uint32_t>(offset >> 32);
+    }
+    return state;
 }
 
 // ---------------------------------------------------------------------------
@@ -312,6 +341,7 @@ rln_forward_kernel(const ForwardParams p) {
     const int warp = threadIdx.x / kWarpSize;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRows;
     grid_dependency_sync();
+    const PhiloxState rng = kDropout ? resolve_philox_state(p) : PhiloxState{0u, 0u, 0u, 0u};
 
     for (int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRows;
          first < p.rows; first += stride) {
@@ -346,12 +376,12 @@ rln_forward_kernel(const ForwardParams p) {
                             + static_cast<uint64_t>(lane + k * kWarpSize);
                         const uint4 random = philox4x32_10(
                             make_uint4(
-                                p.offset_lo,
-                                p.offset_hi,
+                                rng.offset_lo,
+                                rng.offset_hi,
                                 static_cast<uint32_t>(group),
                                 static_cast<uint32_t>(group >> 32)),
-                            p.seed_lo,
-                            p.seed_hi);
+                            rng.seed_lo,
+                            rng.seed_hi);
                         nibble[r][k] =
                             (random.x >= p.threshold ? 1u : 0u)
                             | (random.y >= p.threshold ? 2u : 0u)
@@ -464,6 +494,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
     const int row_in_warp = lane / kLanes;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRowsPerWarp;
     grid_dependency_sync();
+    const PhiloxState rng = kDropout ? resolve_philox_state(p) : PhiloxState{0u, 0u, 0u, 0u};
 
     for (int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRowsPerWarp;
          first < p.rows; first += stride) {
@@ -492,12 +523,12 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
                     + static_cast<uint64_t>(lane_in_row + k * kLanes);
                 const uint4 random = philox4x32_10(
                     make_uint4(
-                        p.offset_lo,
-                        p.offset_hi,
+                        rng.offset_lo,
+                        rng.offset_hi,
                         static_cast<uint32_t>(group),
                         static_cast<uint32_t>(group >> 32)),
-                    p.seed_lo,
-                    p.seed_hi);
+                    rng.seed_lo,
+                    rng.seed_hi);
                 nibble[k] =
                     (random.x >= p.threshold ? 1u : 0u)
                     | (random.y >= p.threshold ? 2u : 0u)

@@ -10,6 +10,7 @@ provided here.
 
 from ._status import BackendStatus
 from .normalization import (
+    allow_graph_capture,
     can_use_residual_layer_norm,
     residual_layer_norm,
     residual_layer_norm_status,
@@ -20,6 +21,7 @@ __version__ = "0.4.0"
 __all__ = [
     "__version__",
     "BackendStatus",
+    "allow_graph_capture",
     "can_use_residual_layer_norm",
     "residual_layer_norm",
     "residual_layer_norm_status",

@@ -97,6 +97,27 @@ def residual_layer_norm_status(device=None):
     return _native_status(resolved.index)
 
 
+def allow_graph_capture(enabled=True):
+    """Let the native dropout be recorded into a CUDA graph.
+
+    Off by default: like the reference (``csrc/residual_layer_norm_kernel.hip:1758-1777``)
+    the native route then raises "... does not support HIP graph capture" when
+    called with active dropout while a stream is capturing.  When enabled, the
+    forward takes torch's graph-safe generator state by pointer, so every
+    replay draws the mask for the generator's state at replay time (replaying
+    after ``torch.cuda.manual_seed(s)`` gives the mask an eager call with the
+    same seed gives).  Returns the previous setting.
+    """
+    from ._normalization_native import _extension
+
+    extension, reason = _extension()
+    if extension is None:
+        raise RuntimeError(f"gfx1010 native extension is unavailable: {reason}")
+    previous = extension.graph_capture_allowed()
+    extension.set_graph_capture_allowed(bool(enabled))
+    return previous
+
+
 def _input_reason(x, branch, weight, bias, dropout_p, eps):
     """First reason the optimised routes cannot take these inputs, else None.
 

@@ -46,7 +46,7 @@ extern "C" {
 #define RLN_ERR_LIMIT (-10)             /* size beyond a documented fixed maximum */
 
 /* ABI version of this header; bumped on any signature change. */
-#define RLN_SM100_ABI_VERSION 1
+#define RLN_SM100_ABI_VERSION 2
 RLN_API int rln_sm100_abi_version(void);
 
 /* Human-readable text for a status code (static storage, never NULL). */
@@ -105,6 +105,40 @@ RLN_API int rln_sm100_forward(
     float eps,
     uint64_t seed,
     uint64_t offset,
+    int64_t row_base,
+    void* stream);
+
+/*
+ * Forward whose Philox (seed, offset) is read from DEVICE memory when the
+ * kernel runs: seed = *device_seed, offset = *device_offset + offset_extra.
+ * Everything else as rln_sm100_forward.
+ *
+ * This is the form a launch recorded into a CUDA graph needs: the reference
+ * refuses dropout under graph capture because its kernel takes the generator
+ * state by value (csrc/residual_layer_norm_kernel.hip:1758-1777); with the
+ * state behind pointers every replay uses whatever the framework has stored
+ * there (torch's graph-safe generator keeps exactly such a seed/offset pair and
+ * hands out an intra-graph offset for each consumer).
+ */
+RLN_API int rln_sm100_forward_device_rng(
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    float* updated,
+    float* normalized,
+    float* mean,
+    float* rstd,
+    uint32_t* dropout_mask,
+    int64_t rows,
+    int32_t hidden,
+    int32_t branch_is_half,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    const int64_t* device_seed,
+    const int64_t* device_offset,
+    uint64_t offset_extra,
     int64_t row_base,
     void* stream);
 
