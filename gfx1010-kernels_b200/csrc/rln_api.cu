@@ -161,6 +161,10 @@ int forward_launch(
     params.device_seed = device_seed;
     params.device_offset = device_offset;
     params.device_offset_extra = device_seed != nullptr ? offset : 0;
+    if (device_seed != nullptr && !vector_ok) {
+        // the device-state kernels exist in the vectorised form only
+        return RLN_ERR_ALIGNMENT;
+    }
 
     int sm_count = 0;
     const int status = current_sm_count(&sm_count);

@@ -4,7 +4,7 @@
 namespace rln {
 namespace {
 
-template <int H, typename BranchT, bool kDropout, bool kAligned>
+template <int H, typename BranchT, bool kDropout, bool kAligned, bool kDeviceRng = false>
 cudaError_t launch_forward_typed(const ForwardParams& params, int sm_count, cudaStream_t stream) {
     constexpr int kWarps = ForwardTune<H>::kWarps;
     constexpr int kRows = ForwardTune<H>::kRows;
@@ -22,14 +22,16 @@ cudaError_t launch_forward_typed(const ForwardParams& params, int sm_count, cuda
     }
     if constexpr (kLanes == kWarpSize) {
         return launch_dependent(
-            rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows, kMinCtas>,
+            rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows, kMinCtas,
+                               kDeviceRng>,
             static_cast<unsigned>(blocks),
             kWarps * kWarpSize,
             stream,
             params);
     } else {
         return launch_dependent(
-            rln_forward_subwarp_kernel<H, BranchT, kDropout, kAligned, kWarps, kLanes, kMinCtas>,
+            rln_forward_subwarp_kernel<H, BranchT, kDropout, kAligned, kWarps, kLanes, kMinCtas,
+                                       kDeviceRng>,
             static_cast<unsigned>(blocks),
             kWarps * kWarpSize,
             stream,
@@ -45,6 +47,16 @@ cudaError_t launch_forward_hidden(
     const ForwardParams& params,
     int sm_count,
     cudaStream_t stream) {
+    if (params.device_seed != nullptr) {
+        // Philox state behind device pointers (graph capture): instantiated for
+        // the vectorised dropout kernels only.
+        if (!dropout || !aligned) {
+            return cudaErrorNotSupported;
+        }
+        return branch_is_half
+            ? launch_forward_typed<H, __half, true, true, true>(params, sm_count, stream)
+            : launch_forward_typed<H, float, true, true, true>(params, sm_count, stream);
+    }
 #define RLN_FWD_CASE(HALF, DROP, ALIGNED)                                                   \
     if (branch_is_half == HALF && dropout == DROP && aligned == ALIGNED) {                  \
         if constexpr (HALF) {                                                               \

@@ -56,7 +56,7 @@ struct ForwardParams {
     // Philox state kept on the device (set when the launch is recorded into a
     // CUDA graph, so that each replay sees the generator's current state):
     // seed = *device_seed, offset = *device_offset + device_offset_extra.
-    // nullptr = use the immediate values above.
+    // Read only by kernels instantiated with kDeviceRng.
     const int64_t* device_seed;
     const int64_t* device_offset;
     uint64_t device_offset_extra;
@@ -133,16 +133,14 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 counter, uint32_t key0, uin
 
 // (seed, offset) of this launch: immediate, or read from device memory.
 __device__ __forceinline__ PhiloxState resolve_philox_state(const ForwardParams& p) {
-    PhiloxState state = {p.seed_lo, p.seed_hi, p.offset_lo, p.offset_hi};
-    if (p.device_seed != nullptr) {
-        const uint64_t seed = static_cast<uint64_t>(__ldg(p.device_seed));
-        const uint64_t offset =
-            static_cast<uint64_t>(__ldg(p.device_offset)) + p.device_offset_extra;
-        state.seed_lo = static_cast<uint32_t>(seed);
-        state.seed_hi = static_cast<uint32_t>(seed >> 32);
-        state.offset_lo = static_cast<uint32_t>(offset);
-        state.offset_hi = static_cast<uint32_t>(offset >> 32);
-    }
+    const uint64_t seed = static_cast<uint64_t>(__ldg(p.device_seed));
+    const uint64_t offset =
+        static_cast<uint64_t>(__ldg(p.device_offset)) + p.device_offset_extra;
+    PhiloxState state;
+    state.seed_lo = static_cast<uint32_t>(seed);
+    state.seed_hi = static_cast<uint32_t>(seed >> 32);
+    state.offset_lo = static_cast<uint32_t>(offset);
+    state.offset_hi = static_cast<uint32_t>(offset >> 32);
     return state;
 }
 
@@ -327,7 +325,7 @@ __device__ __forceinline__ float drop_one(float b, bool keep, float scale) {
 // Forward.  grid-stride over groups of kRows consecutive rows per warp.
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kRows,
-          int kMinCtas = 1>
+          int kMinCtas = 1, bool kDeviceRng = false>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_kernel(const ForwardParams p) {
     static_assert(H % 128 == 0, "hidden must be a multiple of 128");
@@ -341,7 +339,12 @@ rln_forward_kernel(const ForwardParams p) {
     const int warp = threadIdx.x / kWarpSize;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRows;
     grid_dependency_sync();
-    const PhiloxState rng = kDropout ? resolve_philox_state(p) : PhiloxState{0u, 0u, 0u, 0u};
+    // Immediate state: the four words stay kernel-parameter (constant-bank)
+    // operands.  Device state (graph capture): two loads, four registers.
+    PhiloxState rng = {p.seed_lo, p.seed_hi, p.offset_lo, p.offset_hi};
+    if constexpr (kDropout && kDeviceRng) {
+        rng = resolve_philox_state(p);
+    }
 
     for (int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRows;
          first < p.rows; first += stride) {
@@ -476,7 +479,7 @@ rln_forward_kernel(const ForwardParams p) {
 // stores are predicated, shuffles are executed by the whole warp.
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kLanes,
-          int kMinCtas = 1>
+          int kMinCtas = 1, bool kDeviceRng = false>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_subwarp_kernel(const ForwardParams p) {
     static_assert(kLanes == 8 || kLanes == 16, "a row is owned by 8 or 16 lanes");
@@ -494,7 +497,12 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
     const int row_in_warp = lane / kLanes;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRowsPerWarp;
     grid_dependency_sync();
-    const PhiloxState rng = kDropout ? resolve_philox_state(p) : PhiloxState{0u, 0u, 0u, 0u};
+    // Immediate state: the four words stay kernel-parameter (constant-bank)
+    // operands.  Device state (graph capture): two loads, four registers.
+    PhiloxState rng = {p.seed_lo, p.seed_hi, p.offset_lo, p.offset_hi};
+    if constexpr (kDropout && kDeviceRng) {
+        rng = resolve_philox_state(p);
+    }
 
     for (int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRowsPerWarp;
          first < p.rows; first += stride) {

@@ -118,7 +118,9 @@ RLN_API int rln_sm100_forward(
  * state by value (csrc/residual_layer_norm_kernel.hip:1758-1777); with the
  * state behind pointers every replay uses whatever the framework has stored
  * there (torch's graph-safe generator keeps exactly such a seed/offset pair and
- * hands out an intra-graph offset for each consumer).
+ * hands out an intra-graph offset for each consumer).  This form needs the
+ * 16-byte pointer alignment of the vectorised kernels (RLN_ERR_ALIGNMENT
+ * otherwise).
  */
 RLN_API int rln_sm100_forward_device_rng(
     const float* x,
