@@ -114,13 +114,11 @@ class ClockSampler:
         self.device_index = device_index
         self.interval = interval
         self.samples = []
-        self.reason_bits = 0
         self.max_mhz = None
         self._stop = threading.Event()
         self._thread = None
         self._nvml = None
         self._handle = None
-        self.marks = []
 
     def _physical_index(self):
         visible = os.environ.get("CUDA_VISIBLE_DEVICES")

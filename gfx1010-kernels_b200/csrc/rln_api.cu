@@ -4,6 +4,8 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "rln_launch.h"
 
 namespace {
@@ -32,23 +34,27 @@ bool aligned_to(const void* pointer, uintptr_t bytes) {
 
 // SM count of the current device, cached per device ordinal.
 int current_sm_count(int* out) {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];
     int device = 0;
     cudaError_t error = cudaGetDevice(&device);
     if (error != cudaSuccess) {
         return cuda_failed(error);
     }
-    if (device >= 0 && device < 64 && cached[device] > 0) {
-        *out = cached[device];
-        return RLN_OK;
+    const bool cacheable = device >= 0 && device < 64;
+    if (cacheable) {
+        const int known = cached[device].load(std::memory_order_relaxed);
+        if (known > 0) {
+            *out = known;
+            return RLN_OK;
+        }
     }
     int count = 0;
     error = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
     if (error != cudaSuccess) {
         return cuda_failed(error);
     }
-    if (device >= 0 && device < 64) {
-        cached[device] = count;
+    if (cacheable) {
+        cached[device].store(count, std::memory_order_relaxed);
     }
     *out = count;
     return RLN_OK;

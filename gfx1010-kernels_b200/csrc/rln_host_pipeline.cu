@@ -5,6 +5,7 @@
 
 #include <cuda_runtime.h>
 
+#include <initializer_list>
 #include <new>
 
 #include "rln_launch.h"
@@ -200,7 +201,11 @@ extern "C" int rln_sm100_host_pipeline_destroy(RlnHostPipeline* pipeline) {
         }                                              \
     } while (0)
 
-extern "C" int rln_sm100_host_forward_backward(
+namespace {
+
+// Enqueues the whole step on the pipeline's three streams.  Returns at the
+// first failing call; the caller drains the streams in either case.
+int enqueue_step(
     RlnHostPipeline* p,
     const float* x,
     const void* branch,
@@ -322,8 +327,51 @@ extern "C" int rln_sm100_host_forward_backward(
     RLN_TRY(cudaMemcpyAsync(
         grad_parameters, p->total, 2 * hidden * sizeof(float), cudaMemcpyDeviceToHost,
         p->stream_compute));
-    RLN_TRY(cudaStreamSynchronize(p->stream_in));
-    RLN_TRY(cudaStreamSynchronize(p->stream_compute));
-    RLN_TRY(cudaStreamSynchronize(p->stream_out));
+    return RLN_OK;
+}
+
+}  // namespace
+
+extern "C" int rln_sm100_host_forward_backward(
+    RlnHostPipeline* p,
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    const float* grad_updated,
+    const float* grad_normalized,
+    float* updated,
+    float* normalized,
+    float* grad_x,
+    void* grad_branch,
+    float* grad_parameters,
+    int64_t rows,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    uint64_t seed,
+    uint64_t offset,
+    int64_t row_base,
+    int32_t deterministic) {
+    if (p == nullptr) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    const int status = enqueue_step(
+        p, x, branch, weight, bias, grad_updated, grad_normalized, updated, normalized, grad_x,
+        grad_branch, grad_parameters, rows, dropout_active, dropout_p, eps, seed, offset,
+        row_base, deterministic);
+    // Drain the streams whatever happened: copies that were already enqueued
+    // still target the caller's host buffers and must not outlive this call.
+    const cudaError_t drained_in = cudaStreamSynchronize(p->stream_in);
+    const cudaError_t drained_compute = cudaStreamSynchronize(p->stream_compute);
+    const cudaError_t drained_out = cudaStreamSynchronize(p->stream_out);
+    if (status != RLN_OK) {
+        return status;
+    }
+    for (const cudaError_t error : {drained_in, drained_compute, drained_out}) {
+        if (error != cudaSuccess) {
+            return rln::record_cuda_error(error);
+        }
+    }
     return RLN_OK;
 }

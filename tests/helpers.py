@@ -8,7 +8,7 @@ import torch
 from oracle import rln_oracle
 
 # Tolerances (|actual - expected| <= atol + rtol * |expected|).
-UPDATED_TOL = dict(rtol=0.0, atol=0.0)           # exact: one fp32 add of identical operands
+# `updated` is compared with torch.equal: one fp32 add of identical operands is exact.
 NORMALIZED_TOL = dict(rtol=1e-5, atol=1e-6)      # vs the torch decomposition with the kernel's mask
 GRAD_X_TOL = dict(rtol=1e-5, atol=1e-5)
 GRAD_BRANCH_HALF_TOL = dict(rtol=2e-3, atol=1e-5)  # one fp16 rounding of an fp32-close value
