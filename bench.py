@@ -53,6 +53,13 @@ WORKLOADS = {
     "c3_h768": (32768, 768, torch.float16, 0.1),
     "c3_h1024": (32768, 1024, torch.float16, 0.1),
     "c5_64x4096x1024": (262144, 1024, torch.float16, 0.1),
+    # the ragged small-hidden parity shapes and two variants of the headline size
+    "c2_3x1367x128_fp32": (3 * 1367, 128, torch.float32, 0.15),
+    "c2_5x817x256_fp32": (5 * 817, 256, torch.float32, 0.15),
+    "h768_64Mi_fp32_branch": (87381, 768, torch.float32, 0.1),
+    "h768_64Mi_no_dropout": (87381, 768, torch.float16, 0.0),
+    "h128_64Mi": (524288, 128, torch.float16, 0.1),
+    "h256_64Mi": (262144, 256, torch.float16, 0.1),
 }
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch from
 # the ncu capture summarised in profiles/rln_backward_kernel_h768_64Mi.md, per workload.
@@ -447,8 +454,8 @@ def run_native_arm(args, rank, local_rank, world):
         peak, peak_kind = measured_peak_gbs()
         total_rows = rows * world
         value = total_rows * args.steps / (elapsed_ms * 1e-3)
-        fwd_bytes = forward_bytes_per_row(hidden, branch_bytes, True) * rows
-        bwd_bytes = backward_bytes_per_row(hidden, branch_bytes, True) * rows
+        fwd_bytes = forward_bytes_per_row(hidden, branch_bytes, dropout_p > 0) * rows
+        bwd_bytes = backward_bytes_per_row(hidden, branch_bytes, dropout_p > 0) * rows
         fwd_gbs = fwd_bytes / (forward_ms * 1e-3) / 1e9
         bwd_gbs = bwd_bytes / (backward_ms * 1e-3) / 1e9
         step_gbs = (fwd_bytes + bwd_bytes) * world * args.steps / (elapsed_ms * 1e-3) / 1e9
@@ -484,9 +491,9 @@ def run_native_arm(args, rank, local_rank, world):
             "hbm_frac_of_measured": step_gbs / (peak * world),
             "kernels": {
                 "forward": {"ms": forward_ms, "gbs": fwd_gbs, "bytes_per_row":
-                            forward_bytes_per_row(hidden, branch_bytes, True)},
+                            forward_bytes_per_row(hidden, branch_bytes, dropout_p > 0)},
                 "backward": {"ms": backward_ms, "gbs": bwd_gbs, "bytes_per_row":
-                             backward_bytes_per_row(hidden, branch_bytes, True)},
+                             backward_bytes_per_row(hidden, branch_bytes, dropout_p > 0)},
             },
             "roofline": {
                 "kernel": "rln_backward_kernel",
