@@ -61,8 +61,8 @@ WORKLOADS = {
     "h128_64Mi": (524288, 128, torch.float16, 0.1),
     "h256_64Mi": (262144, 256, torch.float16, 0.1),
 }
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch from
-# the ncu capture summarised in profiles/rln_backward_kernel_h768_64Mi.md, per workload.
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch,
+# taken from an ncu capture of that workload (two launches, --set full), per workload.
 NCU_BACKWARD_TRAFFIC_BYTES = {"h768_64Mi": 814_416_128 + 351_629_824}
 CPU_SAMPLE_ROWS = 8192
 EPS = 1e-5

@@ -74,7 +74,7 @@ def draw_inputs(shape, hidden, branch_dtype, seed):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="checkout of the reference project")
     arguments = parser.parse_args()
     sys.path.insert(0, arguments.reference)
     import gfx1010_kernels.normalization as reference  # the reference package
