@@ -341,9 +341,10 @@ rln_forward_kernel(const ForwardParams p) {
     const int warp = threadIdx.x / kWarpSize;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRows;
     grid_dependency_sync();
-    // Immediate state: the four words stay kernel-parameter (constant-bank)
-    // operands.  Device state (graph capture): two loads, four registers.
-    PhiloxState rng = {p.seed_lo, p.seed_hi, p.offset_lo, p.offset_hi};
+    // Device state (graph capture): two loads, four registers.  Immediate
+    // state: the four words are used straight from the kernel parameters
+    // (constant-bank operands), see the Philox call below.
+    PhiloxState rng = {0u, 0u, 0u, 0u};
     if constexpr (kDropout && kDeviceRng) {
         rng = resolve_philox_state(p);
     }
@@ -381,12 +382,12 @@ rln_forward_kernel(const ForwardParams p) {
                             + static_cast<uint64_t>(lane + k * kWarpSize);
                         const uint4 random = philox4x32_10(
                             make_uint4(
-                                rng.offset_lo,
-                                rng.offset_hi,
+                                kDeviceRng ? rng.offset_lo : p.offset_lo,
+                                kDeviceRng ? rng.offset_hi : p.offset_hi,
                                 static_cast<uint32_t>(group),
                                 static_cast<uint32_t>(group >> 32)),
-                            rng.seed_lo,
-                            rng.seed_hi);
+                            kDeviceRng ? rng.seed_lo : p.seed_lo,
+                            kDeviceRng ? rng.seed_hi : p.seed_hi);
                         nibble[r][k] =
                             (random.x >= p.threshold ? 1u : 0u)
                             | (random.y >= p.threshold ? 2u : 0u)
@@ -499,9 +500,10 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
     const int row_in_warp = lane / kLanes;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRowsPerWarp;
     grid_dependency_sync();
-    // Immediate state: the four words stay kernel-parameter (constant-bank)
-    // operands.  Device state (graph capture): two loads, four registers.
-    PhiloxState rng = {p.seed_lo, p.seed_hi, p.offset_lo, p.offset_hi};
+    // Device state (graph capture): two loads, four registers.  Immediate
+    // state: the four words are used straight from the kernel parameters
+    // (constant-bank operands), see the Philox call below.
+    PhiloxState rng = {0u, 0u, 0u, 0u};
     if constexpr (kDropout && kDeviceRng) {
         rng = resolve_philox_state(p);
     }
@@ -533,12 +535,12 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
                     + static_cast<uint64_t>(lane_in_row + k * kLanes);
                 const uint4 random = philox4x32_10(
                     make_uint4(
-                        rng.offset_lo,
-                        rng.offset_hi,
+                        kDeviceRng ? rng.offset_lo : p.offset_lo,
+                        kDeviceRng ? rng.offset_hi : p.offset_hi,
                         static_cast<uint32_t>(group),
                         static_cast<uint32_t>(group >> 32)),
-                    rng.seed_lo,
-                    rng.seed_hi);
+                    kDeviceRng ? rng.seed_lo : p.seed_lo,
+                    kDeviceRng ? rng.seed_hi : p.seed_hi);
                 nibble[k] =
                     (random.x >= p.threshold ? 1u : 0u)
                     | (random.y >= p.threshold ? 2u : 0u)
