@@ -209,20 +209,32 @@ __device__ __forceinline__ void stream_store(uint2* p, uint2 v) {
 #endif
 }
 
-template <bool kAligned>
+// kStream selects the streaming cache hints above.  Measured on B200: the
+// backward (three read streams, two write streams) gains ~4 % from them, the
+// forward (two read, three write streams) loses ~1.5 %, so the forward uses
+// plain accesses.
+template <bool kAligned, bool kStream = true>
 __device__ __forceinline__ float4 load_f4(const float* base, int64_t chunk) {
     if constexpr (kAligned) {
-        return stream_load(reinterpret_cast<const float4*>(base) + chunk);
+        if constexpr (kStream) {
+            return stream_load(reinterpret_cast<const float4*>(base) + chunk);
+        } else {
+            return *(reinterpret_cast<const float4*>(base) + chunk);
+        }
     } else {
         const float* p = base + chunk * 4;
         return make_float4(p[0], p[1], p[2], p[3]);
     }
 }
 
-template <bool kAligned>
+template <bool kAligned, bool kStream = true>
 __device__ __forceinline__ void store_f4(float* base, int64_t chunk, float4 v) {
     if constexpr (kAligned) {
-        stream_store(reinterpret_cast<float4*>(base) + chunk, v);
+        if constexpr (kStream) {
+            stream_store(reinterpret_cast<float4*>(base) + chunk, v);
+        } else {
+            *(reinterpret_cast<float4*>(base) + chunk) = v;
+        }
     } else {
         float* p = base + chunk * 4;
         p[0] = v.x;
@@ -257,9 +269,9 @@ struct BranchIO;
 
 template <>
 struct BranchIO<float> {
-    template <bool kAligned>
+    template <bool kAligned, bool kStream = true>
     static __device__ __forceinline__ float4 load(const void* base, int64_t chunk) {
-        return load_f4<kAligned>(static_cast<const float*>(base), chunk);
+        return load_f4<kAligned, kStream>(static_cast<const float*>(base), chunk);
     }
     template <bool kAligned>
     static __device__ __forceinline__ void store(void* base, int64_t chunk, float4 v) {
@@ -270,10 +282,11 @@ struct BranchIO<float> {
 
 template <>
 struct BranchIO<__half> {
-    template <bool kAligned>
+    template <bool kAligned, bool kStream = true>
     static __device__ __forceinline__ float4 load(const void* base, int64_t chunk) {
         if constexpr (kAligned) {
-            const uint2 raw = stream_load(static_cast<const uint2*>(base) + chunk);
+            const uint2 raw = kStream ? stream_load(static_cast<const uint2*>(base) + chunk)
+                                      : *(static_cast<const uint2*>(base) + chunk);
             const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
             const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
             return make_float4(lo.x, lo.y, hi.x, hi.y);
@@ -363,8 +376,8 @@ rln_forward_kernel(const ForwardParams p) {
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
                     const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
-                    u[r][k] = load_f4<kAligned>(p.x, chunk);
-                    b[r][k] = IO::template load<kAligned>(p.branch, chunk);
+                    u[r][k] = load_f4<kAligned, false>(p.x, chunk);
+                    b[r][k] = IO::template load<kAligned, false>(p.branch, chunk);
                 }
             }
         }
@@ -423,7 +436,7 @@ rln_forward_kernel(const ForwardParams p) {
                 value.w = __fadd_rn(value.w, dropped.w);
                 u[r][k] = value;
                 const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
-                store_f4<kAligned>(p.updated, chunk, value);
+                store_f4<kAligned, false>(p.updated, chunk, value);
                 sum += (value.x + value.y) + (value.z + value.w);
             }
             const float row_mean = warp_sum(sum) * kInvH;
@@ -452,7 +465,7 @@ rln_forward_kernel(const ForwardParams p) {
                 out.y = (u[r][k].y - row_mean) * row_rstd * gamma.y + beta.y;
                 out.z = (u[r][k].z - row_mean) * row_rstd * gamma.z + beta.z;
                 out.w = (u[r][k].w - row_mean) * row_rstd * gamma.w + beta.w;
-                store_f4<kAligned>(p.normalized, row * kChunksPerRow + pchunk, out);
+                store_f4<kAligned, false>(p.normalized, row * kChunksPerRow + pchunk, out);
             }
             if constexpr (kDropout) {
                 // chunk c = lane + 32k covers columns 4c..4c+3 -> nibble
@@ -523,8 +536,8 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             nibble[k] = 0u;
             if (valid) {
                 const int64_t chunk = row * kChunksPerRow + lane_in_row + k * kLanes;
-                u[k] = load_f4<kAligned>(p.x, chunk);
-                b[k] = IO::template load<kAligned>(p.branch, chunk);
+                u[k] = load_f4<kAligned, false>(p.x, chunk);
+                b[k] = IO::template load<kAligned, false>(p.branch, chunk);
             }
         }
         if constexpr (kDropout) {
@@ -567,7 +580,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             value.w = __fadd_rn(value.w, dropped.w);
             u[k] = value;
             if (valid) {
-                store_f4<kAligned>(
+                store_f4<kAligned, false>(
                     p.updated, row * kChunksPerRow + lane_in_row + k * kLanes, value);
             }
             sum += (value.x + value.y) + (value.z + value.w);
@@ -606,7 +619,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             out.z = (u[k].z - row_mean) * row_rstd * gamma.z + beta.z;
             out.w = (u[k].w - row_mean) * row_rstd * gamma.w + beta.w;
             if (valid) {
-                store_f4<kAligned>(p.normalized, row * kChunksPerRow + pchunk, out);
+                store_f4<kAligned, false>(p.normalized, row * kChunksPerRow + pchunk, out);
             }
         }
         if constexpr (kDropout) {

@@ -31,7 +31,8 @@ struct ForwardTune {
     static constexpr int kLanes = H <= 128 ? 8 : (H <= 256 ? 16 : 32);
     static constexpr int kWarps = 4;
     static constexpr int kRows = 1;
-    static constexpr int kMinCtas = H <= 256 ? 6 : (H <= 384 ? 8 : (H <= 512 ? 6 : 4));
+    static constexpr int kMinCtas =
+        H <= 256 ? 6 : (H <= 384 ? 8 : (H <= 512 ? 6 : (H <= 768 ? 5 : 4)));
     static constexpr bool kPersistent = false;
 };
 
