@@ -210,9 +210,10 @@ __device__ __forceinline__ void stream_store(uint2* p, uint2 v) {
 }
 
 // kStream selects the streaming cache hints above.  Measured on B200: the
-// backward (three read streams, two write streams) gains ~4 % from them, the
-// forward (two read, three write streams) loses ~1.5 %, so the forward uses
-// plain accesses.
+// backward gains ~4 % from them.  The forward alone, in short bursts, is
+// ~1.5 % faster with plain accesses, but inside a sustained forward+backward
+// chain (power-capped clocks) the hints are 0.25 % ahead, so both kernels use
+// them; the forward kernels keep the choice as a template parameter.
 template <bool kAligned, bool kStream = true>
 __device__ __forceinline__ float4 load_f4(const float* base, int64_t chunk) {
     if constexpr (kAligned) {
@@ -340,7 +341,7 @@ __device__ __forceinline__ float drop_one(float b, bool keep, float scale) {
 // Forward.  grid-stride over groups of kRows consecutive rows per warp.
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kRows,
-          int kMinCtas = 1, bool kDeviceRng = false>
+          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = true>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_kernel(const ForwardParams p) {
     static_assert(H % 128 == 0, "hidden must be a multiple of 128");
@@ -376,8 +377,8 @@ rln_forward_kernel(const ForwardParams p) {
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
                     const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
-                    u[r][k] = load_f4<kAligned, false>(p.x, chunk);
-                    b[r][k] = IO::template load<kAligned, false>(p.branch, chunk);
+                    u[r][k] = load_f4<kAligned, kStreamHints>(p.x, chunk);
+                    b[r][k] = IO::template load<kAligned, kStreamHints>(p.branch, chunk);
                 }
             }
         }
@@ -436,7 +437,7 @@ rln_forward_kernel(const ForwardParams p) {
                 value.w = __fadd_rn(value.w, dropped.w);
                 u[r][k] = value;
                 const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
-                store_f4<kAligned, false>(p.updated, chunk, value);
+                store_f4<kAligned, kStreamHints>(p.updated, chunk, value);
                 sum += (value.x + value.y) + (value.z + value.w);
             }
             const float row_mean = warp_sum(sum) * kInvH;
@@ -465,7 +466,7 @@ rln_forward_kernel(const ForwardParams p) {
                 out.y = (u[r][k].y - row_mean) * row_rstd * gamma.y + beta.y;
                 out.z = (u[r][k].z - row_mean) * row_rstd * gamma.z + beta.z;
                 out.w = (u[r][k].w - row_mean) * row_rstd * gamma.w + beta.w;
-                store_f4<kAligned, false>(p.normalized, row * kChunksPerRow + pchunk, out);
+                store_f4<kAligned, kStreamHints>(p.normalized, row * kChunksPerRow + pchunk, out);
             }
             if constexpr (kDropout) {
                 // chunk c = lane + 32k covers columns 4c..4c+3 -> nibble
@@ -495,7 +496,7 @@ rln_forward_kernel(const ForwardParams p) {
 // stores are predicated, shuffles are executed by the whole warp.
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kLanes,
-          int kMinCtas = 1, bool kDeviceRng = false>
+          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = true>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_subwarp_kernel(const ForwardParams p) {
     static_assert(kLanes == 8 || kLanes == 16, "a row is owned by 8 or 16 lanes");
@@ -536,8 +537,8 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             nibble[k] = 0u;
             if (valid) {
                 const int64_t chunk = row * kChunksPerRow + lane_in_row + k * kLanes;
-                u[k] = load_f4<kAligned, false>(p.x, chunk);
-                b[k] = IO::template load<kAligned, false>(p.branch, chunk);
+                u[k] = load_f4<kAligned, kStreamHints>(p.x, chunk);
+                b[k] = IO::template load<kAligned, kStreamHints>(p.branch, chunk);
             }
         }
         if constexpr (kDropout) {
@@ -580,7 +581,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             value.w = __fadd_rn(value.w, dropped.w);
             u[k] = value;
             if (valid) {
-                store_f4<kAligned, false>(
+                store_f4<kAligned, kStreamHints>(
                     p.updated, row * kChunksPerRow + lane_in_row + k * kLanes, value);
             }
             sum += (value.x + value.y) + (value.z + value.w);
@@ -619,7 +620,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             out.z = (u[k].z - row_mean) * row_rstd * gamma.z + beta.z;
             out.w = (u[k].w - row_mean) * row_rstd * gamma.w + beta.w;
             if (valid) {
-                store_f4<kAligned, false>(p.normalized, row * kChunksPerRow + pchunk, out);
+                store_f4<kAligned, kStreamHints>(p.normalized, row * kChunksPerRow + pchunk, out);
             }
         }
         if constexpr (kDropout) {
