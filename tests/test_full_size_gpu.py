@@ -197,3 +197,62 @@ def test_row_sharded_64x4096x1024_reproduces_unsharded_rows():
         total += back[3].double()
     assert_parameters_close(whole_back[3][0], total[0], rows, "grad_weight")
     assert_parameters_close(whole_back[3][1], total[1], rows, "grad_bias")
+
+
+def test_more_than_2_to_the_31_elements_is_indexed_with_64_bits():
+    """2,100,000 x 1,024 = 2.15e9 elements per tensor: element offsets no longer
+    fit in 32 bits.  The last rows of the big call must equal a small call on
+    those rows alone (given the same global row offset), forward and backward."""
+    rows, hidden, p, tail = 2_100_000, 1024, 0.1, 96
+    free_bytes = torch.cuda.mem_get_info()[0]
+    if free_bytes < 80 * (1 << 30):
+        pytest.skip("needs about 70 GB of free device memory")
+    generator = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(rows, hidden, device="cuda", generator=generator)
+    branch = torch.randn(rows, hidden, device="cuda", generator=generator, dtype=torch.float16)
+    weight = 1.0 + 0.1 * torch.randn(hidden, device="cuda", generator=generator)
+    bias = 0.1 * torch.randn(hidden, device="cuda", generator=generator)
+    assert x.numel() > 2 ** 31
+    big = cabi.forward(x, branch, weight, bias, p, 1e-5, True, seed=2, offset=8)
+    assert big[0] == 0, cabi.status_text(big[0])
+    begin = rows - tail
+    small = cabi.forward(
+        x[begin:], branch[begin:], weight, bias, p, 1e-5, True, seed=2, offset=8, row_base=begin
+    )
+    assert small[0] == 0
+    words = hidden // 32
+    assert torch.equal(big[1][begin:], small[1])
+    assert torch.equal(big[2][begin:], small[2])
+    assert torch.equal(big[3][begin:], small[3])
+    assert torch.equal(big[4][begin:], small[4])
+    assert torch.equal(big[5][begin * words:], small[5])
+    # rows just below the 2**31-element boundary and the very first rows too
+    boundary = (2 ** 31) // hidden
+    for lo in (0, boundary - 8):
+        piece = cabi.forward(
+            x[lo:lo + 16], branch[lo:lo + 16], weight, bias, p, 1e-5, True,
+            seed=2, offset=8, row_base=lo,
+        )
+        assert torch.equal(big[1][lo:lo + 16], piece[1])
+        assert torch.equal(big[5][lo * words:(lo + 16) * words], piece[5])
+    keep_fraction = unpack_mask_device(big[5][-words * 4096:], 4096, hidden).float().mean().item()
+    assert abs(keep_fraction - 0.9) < 4 * (0.09 / (4096 * hidden)) ** 0.5
+
+    _, updated, _, mean, rstd, mask = big
+    del x, branch, big, small, piece
+    torch.cuda.empty_cache()
+    grad_updated = torch.randn(rows, hidden, device="cuda", generator=generator)
+    grad_normalized = torch.randn(rows, hidden, device="cuda", generator=generator)
+    whole = cabi.backward(grad_updated, grad_normalized, updated, weight, mean, rstd, mask,
+                          p, True, torch.float16, True)
+    assert whole[0] == 0, cabi.status_text(whole[0])
+    part = cabi.backward(
+        grad_updated[begin:], grad_normalized[begin:], updated[begin:], weight, mean[begin:],
+        rstd[begin:], mask[begin * words:], p, True, torch.float16, True,
+    )
+    assert part[0] == 0
+    torch.cuda.synchronize()
+    assert torch.equal(whole[1][begin:], part[1])
+    assert torch.equal(whole[2][begin:], part[2])
+    expected_bias = grad_normalized.sum(dim=0, dtype=torch.float64)
+    assert_parameters_close(whole[3][1], expected_bias, rows, "grad_bias")
