@@ -58,12 +58,15 @@ WORKLOADS = {
     "c2_5x817x256_fp32": (5 * 817, 256, torch.float32, 0.15),
     "h768_64Mi_fp32_branch": (87381, 768, torch.float32, 0.1),
     "h768_64Mi_no_dropout": (87381, 768, torch.float16, 0.0),
+    "h768_64Mi_bf16_branch": (87381, 768, torch.bfloat16, 0.1),
     "h128_64Mi": (524288, 128, torch.float16, 0.1),
     "h256_64Mi": (262144, 256, torch.float16, 0.1),
 }
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch,
 # taken from an ncu capture of that workload (two launches, --set full), per workload.
 NCU_BACKWARD_TRAFFIC_BYTES = {"h768_64Mi": 814_416_128 + 351_629_824}
+# the extension's branch type codes (False/0 float32, True/1 float16, 2 bfloat16)
+BRANCH_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 CPU_SAMPLE_ROWS = 8192
 EPS = 1e-5
 
@@ -298,7 +301,7 @@ def run_native_arm(args, rank, local_rank, world):
         )
 
     rows, hidden, branch_dtype, dropout_p = WORKLOADS[args.workload]
-    branch_bytes = 2 if branch_dtype == torch.float16 else 4
+    branch_bytes = 4 if branch_dtype == torch.float32 else 2
     host = draw_inputs(rows, hidden, branch_dtype, seed=rank)
     x, branch, weight, bias, grad_updated, grad_normalized = (t.to(device) for t in host)
     if world > 1:
@@ -337,7 +340,7 @@ def run_native_arm(args, rank, local_rank, world):
             e1.record()
         gradients = _C.residual_layer_norm_backward(
             grad_updated, grad_normalized, updated, weight, mean, rstd, mask,
-            dropout_p, True, branch_bytes == 2, 128, 64, 256, 1, True,
+            dropout_p, True, BRANCH_CODES[branch_dtype], 128, 64, 256, 1, True,
         )
         if record:
             e2.record()

@@ -28,6 +28,11 @@ bool supported_hidden(int32_t hidden) {
         || hidden == 768 || hidden == 1024;
 }
 
+bool supported_branch(int32_t branch_dtype) {
+    return branch_dtype == RLN_BRANCH_FLOAT32 || branch_dtype == RLN_BRANCH_FLOAT16
+        || branch_dtype == RLN_BRANCH_BFLOAT16;
+}
+
 bool aligned_to(const void* pointer, uintptr_t bytes) {
     return (reinterpret_cast<uintptr_t>(pointer) & (bytes - 1)) == 0;
 }
@@ -87,6 +92,7 @@ extern "C" const char* rln_sm100_status_string(int status) {
         case RLN_ERR_CUDA: return "a CUDA runtime call failed";
         case RLN_ERR_HOST_BUFFERS: return "invalid host-buffer pipeline arguments";
         case RLN_ERR_LIMIT: return "size exceeds a fixed maximum of this entry point";
+        case RLN_ERR_BRANCH_DTYPE: return "branch must use float32, float16 or bfloat16";
         default: return "unknown status";
     }
 }
@@ -107,7 +113,7 @@ int forward_launch(
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -119,6 +125,9 @@ int forward_launch(
     void* stream) {
     if (!supported_hidden(hidden)) {
         return RLN_ERR_HIDDEN_SIZE;
+    }
+    if (!supported_branch(branch_dtype)) {
+        return RLN_ERR_BRANCH_DTYPE;
     }
     if (rows <= 0) {
         return RLN_ERR_ROW_COUNT;
@@ -134,7 +143,7 @@ int forward_launch(
         || (dropout_active && dropout_mask == nullptr)) {
         return RLN_ERR_NULL_POINTER;
     }
-    const uintptr_t branch_element = branch_is_half ? 2 : 4;
+    const uintptr_t branch_element = branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2;
     if (!aligned_to(x, 4) || !aligned_to(branch, branch_element) || !aligned_to(weight, 4)
         || !aligned_to(bias, 4) || !aligned_to(updated, 4) || !aligned_to(normalized, 4)
         || !aligned_to(mean, 4) || !aligned_to(rstd, 4)
@@ -179,7 +188,7 @@ int forward_launch(
     }
     const cudaError_t error = rln::launch_forward(
         hidden,
-        branch_is_half != 0,
+        branch_dtype,
         dropout_active != 0,
         vector_ok,
         params,
@@ -202,7 +211,7 @@ extern "C" int rln_sm100_forward(
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -212,7 +221,7 @@ extern "C" int rln_sm100_forward(
     void* stream) {
     return forward_launch(
         x, branch, weight, bias, updated, normalized, mean, rstd, dropout_mask, rows, hidden,
-        branch_is_half, dropout_active, dropout_p, eps, seed, offset, nullptr, nullptr, row_base,
+        branch_dtype, dropout_active, dropout_p, eps, seed, offset, nullptr, nullptr, row_base,
         stream);
 }
 
@@ -228,7 +237,7 @@ extern "C" int rln_sm100_forward_device_rng(
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -246,7 +255,7 @@ extern "C" int rln_sm100_forward_device_rng(
     }
     return forward_launch(
         x, branch, weight, bias, updated, normalized, mean, rstd, dropout_mask, rows, hidden,
-        branch_is_half, dropout_active, dropout_p, eps, 0, offset_extra,
+        branch_dtype, dropout_active, dropout_p, eps, 0, offset_extra,
         dropout_active ? device_seed : nullptr, dropout_active ? device_offset : nullptr,
         row_base, stream);
 }
@@ -288,13 +297,16 @@ extern "C" int rln_sm100_backward(
     int64_t workspace_bytes,
     int64_t rows,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int32_t dropout_active,
     float dropout_p,
     int32_t deterministic,
     void* stream_pointer) {
     if (!supported_hidden(hidden)) {
         return RLN_ERR_HIDDEN_SIZE;
+    }
+    if (!supported_branch(branch_dtype)) {
+        return RLN_ERR_BRANCH_DTYPE;
     }
     if (rows <= 0) {
         return RLN_ERR_ROW_COUNT;
@@ -307,7 +319,7 @@ extern "C" int rln_sm100_backward(
         || grad_branch == nullptr || (dropout_active && dropout_mask == nullptr)) {
         return RLN_ERR_NULL_POINTER;
     }
-    const uintptr_t branch_element = branch_is_half ? 2 : 4;
+    const uintptr_t branch_element = branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2;
     if (!aligned_to(grad_updated, 4) || !aligned_to(grad_normalized, 4) || !aligned_to(updated, 4)
         || !aligned_to(weight, 4) || !aligned_to(mean, 4) || !aligned_to(rstd, 4)
         || !aligned_to(grad_x, 4) || !aligned_to(grad_branch, branch_element)
@@ -365,7 +377,7 @@ extern "C" int rln_sm100_backward(
     }
     cudaError_t error = rln::launch_backward(
         hidden,
-        branch_is_half != 0,
+        branch_dtype,
         dropout_active != 0,
         parameters,
         vector_ok,

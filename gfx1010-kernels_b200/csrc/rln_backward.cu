@@ -26,32 +26,43 @@ cudaError_t launch_backward_typed(const BackwardParams& params, int grid, cudaSt
         params);
 }
 
-template <int H, bool kAligned>
-cudaError_t launch_backward_hidden(
-    bool branch_is_half,
+template <int H, typename BranchT, bool kAligned>
+cudaError_t launch_backward_branch(
     bool dropout,
     bool parameters,
     const BackwardParams& params,
     int grid,
     cudaStream_t stream) {
-#define RLN_BWD_CASE(HALF, DROP, PARAMS)                                                        \
-    if (branch_is_half == HALF && dropout == DROP && parameters == PARAMS) {                    \
-        if constexpr (HALF) {                                                                   \
-            return launch_backward_typed<H, __half, DROP, PARAMS, kAligned>(params, grid, stream); \
-        } else {                                                                                \
-            return launch_backward_typed<H, float, DROP, PARAMS, kAligned>(params, grid, stream);  \
-        }                                                                                       \
+    if (dropout) {
+        return parameters
+            ? launch_backward_typed<H, BranchT, true, true, kAligned>(params, grid, stream)
+            : launch_backward_typed<H, BranchT, true, false, kAligned>(params, grid, stream);
     }
-    RLN_BWD_CASE(true, true, true)
-    RLN_BWD_CASE(true, true, false)
-    RLN_BWD_CASE(true, false, true)
-    RLN_BWD_CASE(true, false, false)
-    RLN_BWD_CASE(false, true, true)
-    RLN_BWD_CASE(false, true, false)
-    RLN_BWD_CASE(false, false, true)
-    RLN_BWD_CASE(false, false, false)
-#undef RLN_BWD_CASE
-    return cudaErrorInvalidValue;
+    return parameters
+        ? launch_backward_typed<H, BranchT, false, true, kAligned>(params, grid, stream)
+        : launch_backward_typed<H, BranchT, false, false, kAligned>(params, grid, stream);
+}
+
+template <int H, bool kAligned>
+cudaError_t launch_backward_hidden(
+    int branch_kind,
+    bool dropout,
+    bool parameters,
+    const BackwardParams& params,
+    int grid,
+    cudaStream_t stream) {
+    switch (branch_kind) {
+        case 0:
+            return launch_backward_branch<H, float, kAligned>(
+                dropout, parameters, params, grid, stream);
+        case 1:
+            return launch_backward_branch<H, __half, kAligned>(
+                dropout, parameters, params, grid, stream);
+        case 2:
+            return launch_backward_branch<H, __nv_bfloat16, kAligned>(
+                dropout, parameters, params, grid, stream);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace
@@ -70,7 +81,7 @@ int backward_grid(int hidden, int64_t rows, int sm_count) {
 
 cudaError_t launch_backward(
     int hidden,
-    bool branch_is_half,
+    int branch_kind,
     bool dropout,
     bool parameters,
     bool aligned,
@@ -81,9 +92,9 @@ cudaError_t launch_backward(
     case HIDDEN:                                                                             \
         return aligned                                                                       \
             ? launch_backward_hidden<HIDDEN, true>(                                          \
-                  branch_is_half, dropout, parameters, params, grid, stream)                 \
+                  branch_kind, dropout, parameters, params, grid, stream)                 \
             : launch_backward_hidden<HIDDEN, false>(                                         \
-                  branch_is_half, dropout, parameters, params, grid, stream);
+                  branch_kind, dropout, parameters, params, grid, stream);
     switch (hidden) {
         RLN_BWD_HIDDEN(128)
         RLN_BWD_HIDDEN(256)

@@ -86,13 +86,17 @@ extern "C" int rln_sm100_backward_static_scratch(
     float* grad_parameters,
     int64_t rows,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int32_t dropout_active,
     float dropout_p,
     void* stream_pointer) {
     if (!(hidden == 128 || hidden == 256 || hidden == 384 || hidden == 512 || hidden == 768
           || hidden == 1024)) {
         return RLN_ERR_HIDDEN_SIZE;
+    }
+    if (branch_dtype != RLN_BRANCH_FLOAT32 && branch_dtype != RLN_BRANCH_FLOAT16
+        && branch_dtype != RLN_BRANCH_BFLOAT16) {
+        return RLN_ERR_BRANCH_DTYPE;
     }
     if (rows <= 0) {
         return RLN_ERR_ROW_COUNT;
@@ -106,7 +110,7 @@ extern "C" int rln_sm100_backward_static_scratch(
         || (dropout_active && dropout_mask == nullptr)) {
         return RLN_ERR_NULL_POINTER;
     }
-    const uintptr_t branch_element = branch_is_half ? 2 : 4;
+    const uintptr_t branch_element = branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2;
     if (!aligned_to(grad_updated, 4) || !aligned_to(grad_normalized, 4) || !aligned_to(updated, 4)
         || !aligned_to(weight, 4) || !aligned_to(mean, 4) || !aligned_to(rstd, 4)
         || !aligned_to(grad_x, 4) || !aligned_to(grad_branch, branch_element)
@@ -153,7 +157,7 @@ extern "C" int rln_sm100_backward_static_scratch(
     // beyond `grid` and are never read.
     cudaError_t error = rln::launch_backward(
         hidden,
-        branch_is_half != 0,
+        branch_dtype,
         dropout_active != 0,
         /*parameters=*/true,
         vector_ok,

@@ -42,6 +42,28 @@ bool native_hidden(int64_t hidden) {
         || hidden == 768 || hidden == 1024;
 }
 
+// Branch element types: the reference's two (float16, float32) plus bfloat16.
+bool branch_dtype_supported(at::ScalarType type) {
+    return type == at::kHalf || type == at::kFloat || type == at::kBFloat16;
+}
+
+int32_t branch_dtype_code(at::ScalarType type) {
+    if (type == at::kHalf) {
+        return RLN_BRANCH_FLOAT16;
+    }
+    return type == at::kBFloat16 ? RLN_BRANCH_BFLOAT16 : RLN_BRANCH_FLOAT32;
+}
+
+at::ScalarType branch_dtype_from_code(int64_t code) {
+    TORCH_CHECK(
+        code == RLN_BRANCH_FLOAT32 || code == RLN_BRANCH_FLOAT16 || code == RLN_BRANCH_BFLOAT16,
+        "branch_is_half must be False/0 (float32), True/1 (float16) or 2 (bfloat16)");
+    if (code == RLN_BRANCH_FLOAT16) {
+        return at::kHalf;
+    }
+    return code == RLN_BRANCH_BFLOAT16 ? at::kBFloat16 : at::kFloat;
+}
+
 void check_status(int status, const char* what) {
     if (status == RLN_OK) {
         return;
@@ -74,8 +96,7 @@ void check_forward_inputs(
         "all tensors must be on the same HIP device");
     TORCH_CHECK(x.scalar_type() == at::kFloat, "x must use float32");
     TORCH_CHECK(
-        branch.scalar_type() == at::kHalf || branch.scalar_type() == at::kFloat,
-        "branch must use float16 or float32");
+        branch_dtype_supported(branch.scalar_type()), "branch must use float16 or float32");
     TORCH_CHECK(
         weight.scalar_type() == at::kFloat && bias.scalar_type() == at::kFloat,
         "weight and bias must use float32");
@@ -214,14 +235,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> forward_l
     const auto stream = c10::cuda::getCurrentCUDAStream(x.device().index()).stream();
     uint32_t* mask_pointer =
         dropout ? reinterpret_cast<uint32_t*>(dropout_mask.data_ptr<int32_t>()) : nullptr;
-    const int32_t branch_is_half = branch.scalar_type() == at::kHalf ? 1 : 0;
+    const int32_t branch_dtype = branch_dtype_code(branch.scalar_type());
     int status = RLN_OK;
     if (device_seed != nullptr) {
         status = rln_sm100_forward_device_rng(
             x.data_ptr<float>(), branch.data_ptr(), weight.data_ptr<float>(),
             bias.data_ptr<float>(), updated.data_ptr<float>(), normalized.data_ptr<float>(),
             mean.data_ptr<float>(), rstd.data_ptr<float>(), mask_pointer, row_count,
-            static_cast<int32_t>(hidden), branch_is_half, dropout ? 1 : 0,
+            static_cast<int32_t>(hidden), branch_dtype, dropout ? 1 : 0,
             static_cast<float>(dropout_p), static_cast<float>(eps), device_seed, device_offset,
             offset, row_base, stream);
     } else {
@@ -229,7 +250,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> forward_l
             x.data_ptr<float>(), branch.data_ptr(), weight.data_ptr<float>(),
             bias.data_ptr<float>(), updated.data_ptr<float>(), normalized.data_ptr<float>(),
             mean.data_ptr<float>(), rstd.data_ptr<float>(), mask_pointer, row_count,
-            static_cast<int32_t>(hidden), branch_is_half, dropout ? 1 : 0,
+            static_cast<int32_t>(hidden), branch_dtype, dropout ? 1 : 0,
             static_cast<float>(dropout_p), static_cast<float>(eps), seed, offset, row_base,
             stream);
     }
@@ -332,12 +353,15 @@ std::vector<at::Tensor> residual_layer_norm_backward_cuda(
     const at::Tensor& dropout_mask,
     double dropout_p,
     bool training,
-    bool branch_is_half,
+    int64_t branch_is_half,
     int64_t threads,
     int64_t block_rows,
     int64_t parameter_threads,
     int64_t parameter_groups,
     bool compute_parameter_gradients) {
+    // `branch_is_half` keeps the reference's name and position; it is an integer
+    // here so that False/True still mean float32/float16 and 2 selects bfloat16.
+    const at::ScalarType branch_type = branch_dtype_from_code(branch_is_half);
     check_backward_inputs(
         grad_updated,
         grad_normalized,
@@ -360,7 +384,7 @@ std::vector<at::Tensor> residual_layer_norm_backward_cuda(
     auto grad_x = at::empty_like(updated);
     auto grad_branch = at::empty(
         updated.sizes(),
-        updated.options().dtype(branch_is_half ? at::kHalf : at::kFloat));
+        updated.options().dtype(branch_type));
     at::Tensor parameter_gradients;
     at::Tensor grad_weight;
     at::Tensor grad_bias;
@@ -399,7 +423,7 @@ std::vector<at::Tensor> residual_layer_norm_backward_cuda(
         workspace_bytes,
         row_count,
         static_cast<int32_t>(hidden),
-        branch_is_half ? 1 : 0,
+        branch_dtype_code(branch_type),
         dropout ? 1 : 0,
         static_cast<float>(dropout_p),
         deterministic ? 1 : 0,
@@ -437,7 +461,8 @@ class ResidualLayerNormFunction
         ctx->set_materialize_grads(false);
         ctx->saved_data["dropout_p"] = dropout_p;
         ctx->saved_data["training"] = training;
-        ctx->saved_data["branch_is_half"] = branch.scalar_type() == at::kHalf;
+        ctx->saved_data["branch_dtype"] =
+            static_cast<int64_t>(branch_dtype_code(branch.scalar_type()));
         ctx->saved_data["threads"] = threads;
         ctx->saved_data["block_rows"] = block_rows;
         ctx->saved_data["parameter_threads"] = parameter_threads;
@@ -464,7 +489,7 @@ class ResidualLayerNormFunction
             saved[4],
             ctx->saved_data["dropout_p"].toDouble(),
             ctx->saved_data["training"].toBool(),
-            ctx->saved_data["branch_is_half"].toBool(),
+            ctx->saved_data["branch_dtype"].toInt(),
             ctx->saved_data["threads"].toInt(),
             ctx->saved_data["block_rows"].toInt(),
             ctx->saved_data["parameter_threads"].toInt(),

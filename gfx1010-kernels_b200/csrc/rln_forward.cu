@@ -39,9 +39,8 @@ cudaError_t launch_forward_typed(const ForwardParams& params, int sm_count, cuda
     }
 }
 
-template <int H>
-cudaError_t launch_forward_hidden(
-    bool branch_is_half,
+template <int H, typename BranchT>
+cudaError_t launch_forward_branch(
     bool dropout,
     bool aligned,
     const ForwardParams& params,
@@ -53,47 +52,51 @@ cudaError_t launch_forward_hidden(
         if (!dropout || !aligned) {
             return cudaErrorNotSupported;
         }
-        return branch_is_half
-            ? launch_forward_typed<H, __half, true, true, true>(params, sm_count, stream)
-            : launch_forward_typed<H, float, true, true, true>(params, sm_count, stream);
+        return launch_forward_typed<H, BranchT, true, true, true>(params, sm_count, stream);
     }
-#define RLN_FWD_CASE(HALF, DROP, ALIGNED)                                                   \
-    if (branch_is_half == HALF && dropout == DROP && aligned == ALIGNED) {                  \
-        if constexpr (HALF) {                                                               \
-            return launch_forward_typed<H, __half, DROP, ALIGNED>(params, sm_count, stream);          \
-        } else {                                                                            \
-            return launch_forward_typed<H, float, DROP, ALIGNED>(params, sm_count, stream);           \
-        }                                                                                   \
+    if (dropout) {
+        return aligned ? launch_forward_typed<H, BranchT, true, true>(params, sm_count, stream)
+                       : launch_forward_typed<H, BranchT, true, false>(params, sm_count, stream);
     }
-    RLN_FWD_CASE(true, true, true)
-    RLN_FWD_CASE(true, false, true)
-    RLN_FWD_CASE(false, true, true)
-    RLN_FWD_CASE(false, false, true)
-    RLN_FWD_CASE(true, true, false)
-    RLN_FWD_CASE(true, false, false)
-    RLN_FWD_CASE(false, true, false)
-    RLN_FWD_CASE(false, false, false)
-#undef RLN_FWD_CASE
-    return cudaErrorInvalidValue;
+    return aligned ? launch_forward_typed<H, BranchT, false, true>(params, sm_count, stream)
+                   : launch_forward_typed<H, BranchT, false, false>(params, sm_count, stream);
+}
+
+template <int H>
+cudaError_t launch_forward_hidden(
+    int branch_kind,
+    bool dropout,
+    bool aligned,
+    const ForwardParams& params,
+    int sm_count,
+    cudaStream_t stream) {
+    switch (branch_kind) {
+        case 0: return launch_forward_branch<H, float>(dropout, aligned, params, sm_count, stream);
+        case 1: return launch_forward_branch<H, __half>(dropout, aligned, params, sm_count, stream);
+        case 2:
+            return launch_forward_branch<H, __nv_bfloat16>(
+                dropout, aligned, params, sm_count, stream);
+        default: return cudaErrorInvalidValue;
+    }
 }
 
 }  // namespace
 
 cudaError_t launch_forward(
     int hidden,
-    bool branch_is_half,
+    int branch_kind,
     bool dropout,
     bool aligned,
     const ForwardParams& params,
     int sm_count,
     cudaStream_t stream) {
     switch (hidden) {
-        case 128: return launch_forward_hidden<128>(branch_is_half, dropout, aligned, params, sm_count, stream);
-        case 256: return launch_forward_hidden<256>(branch_is_half, dropout, aligned, params, sm_count, stream);
-        case 384: return launch_forward_hidden<384>(branch_is_half, dropout, aligned, params, sm_count, stream);
-        case 512: return launch_forward_hidden<512>(branch_is_half, dropout, aligned, params, sm_count, stream);
-        case 768: return launch_forward_hidden<768>(branch_is_half, dropout, aligned, params, sm_count, stream);
-        case 1024: return launch_forward_hidden<1024>(branch_is_half, dropout, aligned, params, sm_count, stream);
+        case 128: return launch_forward_hidden<128>(branch_kind, dropout, aligned, params, sm_count, stream);
+        case 256: return launch_forward_hidden<256>(branch_kind, dropout, aligned, params, sm_count, stream);
+        case 384: return launch_forward_hidden<384>(branch_kind, dropout, aligned, params, sm_count, stream);
+        case 512: return launch_forward_hidden<512>(branch_kind, dropout, aligned, params, sm_count, stream);
+        case 768: return launch_forward_hidden<768>(branch_kind, dropout, aligned, params, sm_count, stream);
+        case 1024: return launch_forward_hidden<1024>(branch_kind, dropout, aligned, params, sm_count, stream);
         default: return cudaErrorInvalidValue;
     }
 }

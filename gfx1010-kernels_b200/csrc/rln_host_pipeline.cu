@@ -52,7 +52,7 @@ struct Slot {
 struct RlnHostPipeline {
     int device = 0;
     int32_t hidden = 0;
-    int32_t branch_is_half = 0;
+    int32_t branch_dtype = 0;
     int64_t chunk_rows = 0;
     int32_t depth = 0;
     int64_t workspace_bytes = 0;
@@ -108,7 +108,7 @@ void release(RlnHostPipeline* p) {
 
 bool allocate(RlnHostPipeline* p) {
     const size_t elements = static_cast<size_t>(p->chunk_rows) * p->hidden;
-    const size_t branch_bytes = elements * (p->branch_is_half ? 2 : 4);
+    const size_t branch_bytes = elements * (p->branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2);
     RLN_TRY(cudaStreamCreateWithFlags(&p->stream_in, cudaStreamNonBlocking));
     RLN_TRY(cudaStreamCreateWithFlags(&p->stream_compute, cudaStreamNonBlocking));
     RLN_TRY(cudaStreamCreateWithFlags(&p->stream_out, cudaStreamNonBlocking));
@@ -144,7 +144,7 @@ bool allocate(RlnHostPipeline* p) {
 extern "C" int rln_sm100_host_pipeline_create(
     RlnHostPipeline** pipeline,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int64_t chunk_rows,
     int32_t depth) {
     if (pipeline == nullptr) {
@@ -153,6 +153,10 @@ extern "C" int rln_sm100_host_pipeline_create(
     *pipeline = nullptr;
     if (chunk_rows <= 0 || chunk_rows > (1 << 24) || depth < 2 || depth > kMaxDepth) {
         return RLN_ERR_HOST_BUFFERS;
+    }
+    if (branch_dtype != RLN_BRANCH_FLOAT32 && branch_dtype != RLN_BRANCH_FLOAT16
+        && branch_dtype != RLN_BRANCH_BFLOAT16) {
+        return RLN_ERR_BRANCH_DTYPE;
     }
     // the deterministic workspace for the largest chunk; also validates hidden
     const int64_t workspace_bytes = rln_sm100_backward_workspace_bytes(chunk_rows, hidden, 1);
@@ -169,7 +173,7 @@ extern "C" int rln_sm100_host_pipeline_create(
         return rln::record_cuda_error(device_error);
     }
     p->hidden = hidden;
-    p->branch_is_half = branch_is_half ? 1 : 0;
+    p->branch_dtype = branch_dtype;
     p->chunk_rows = chunk_rows;
     p->depth = depth;
     p->workspace_bytes = workspace_bytes;
@@ -247,7 +251,7 @@ int enqueue_step(
         return RLN_ERR_HOST_BUFFERS;
     }
     const int64_t hidden = p->hidden;
-    const size_t branch_element = p->branch_is_half ? 2 : 4;
+    const size_t branch_element = p->branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2;
     const char* branch_bytes = static_cast<const char*>(branch);
     char* grad_branch_bytes = static_cast<char*>(grad_branch);
 
@@ -290,7 +294,7 @@ int enqueue_step(
         }
         int status = rln_sm100_forward(
             slot.x, slot.branch, p->weight, p->bias, slot.updated, slot.normalized, slot.mean,
-            slot.rstd, slot.mask, count, p->hidden, p->branch_is_half, dropout_active, dropout_p,
+            slot.rstd, slot.mask, count, p->hidden, p->branch_dtype, dropout_active, dropout_p,
             eps, seed, offset, row_base + begin, p->stream_compute);
         if (status != RLN_OK) {
             return status;
@@ -298,7 +302,7 @@ int enqueue_step(
         status = rln_sm100_backward(
             slot.grad_updated, slot.grad_normalized, slot.updated, p->weight, slot.mean,
             slot.rstd, slot.mask, slot.grad_x, slot.grad_branch, slot.grad_parameters,
-            slot.workspace, p->workspace_bytes, count, p->hidden, p->branch_is_half,
+            slot.workspace, p->workspace_bytes, count, p->hidden, p->branch_dtype,
             dropout_active, dropout_p, deterministic, p->stream_compute);
         if (status != RLN_OK) {
             return status;

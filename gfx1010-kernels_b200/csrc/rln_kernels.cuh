@@ -25,6 +25,7 @@
 // layout and the single-pass backward do not.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -316,6 +317,51 @@ struct BranchIO<__half> {
     }
     static __device__ __forceinline__ float round(float v) {
         return __half2float(__float2half_rn(v));
+    }
+};
+
+// bfloat16 branch (what mixed-precision training on this hardware produces;
+// the reference, written for a GPU without bf16, stops at fp16).  Same access
+// pattern as fp16: four elements = one 64-bit word per lane.
+template <>
+struct BranchIO<__nv_bfloat16> {
+    template <bool kAligned, bool kStream = true>
+    static __device__ __forceinline__ float4 load(const void* base, int64_t chunk) {
+        if constexpr (kAligned) {
+            const uint2 raw = kStream ? stream_load(static_cast<const uint2*>(base) + chunk)
+                                      : *(static_cast<const uint2*>(base) + chunk);
+            // a bfloat16 is the upper half of the float32 with the same value
+            return make_float4(
+                __uint_as_float(raw.x << 16),
+                __uint_as_float(raw.x & 0xffff0000u),
+                __uint_as_float(raw.y << 16),
+                __uint_as_float(raw.y & 0xffff0000u));
+        } else {
+            const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(base) + chunk * 4;
+            return make_float4(
+                __bfloat162float(p[0]), __bfloat162float(p[1]), __bfloat162float(p[2]),
+                __bfloat162float(p[3]));
+        }
+    }
+    template <bool kAligned>
+    static __device__ __forceinline__ void store(void* base, int64_t chunk, float4 v) {
+        if constexpr (kAligned) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
+            uint2 raw;
+            raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+            raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+            stream_store(static_cast<uint2*>(base) + chunk, raw);
+        } else {
+            __nv_bfloat16* p = static_cast<__nv_bfloat16*>(base) + chunk * 4;
+            p[0] = __float2bfloat16_rn(v.x);
+            p[1] = __float2bfloat16_rn(v.y);
+            p[2] = __float2bfloat16_rn(v.z);
+            p[3] = __float2bfloat16_rn(v.w);
+        }
+    }
+    static __device__ __forceinline__ float round(float v) {
+        return __bfloat162float(__float2bfloat16_rn(v));
     }
 };
 

@@ -82,9 +82,10 @@ int record_cuda_error(cudaError_t error);
 // arguments; also the number of [2, hidden] partials in deterministic mode).
 int backward_grid(int hidden, int64_t rows, int sm_count);
 
+// branch_kind: RLN_BRANCH_FLOAT32 / FLOAT16 / BFLOAT16 (0 / 1 / 2).
 cudaError_t launch_forward(
     int hidden,
-    bool branch_is_half,
+    int branch_kind,
     bool dropout,
     bool aligned,
     const ForwardParams& params,
@@ -93,7 +94,7 @@ cudaError_t launch_forward(
 
 cudaError_t launch_backward(
     int hidden,
-    bool branch_is_half,
+    int branch_kind,
     bool dropout,
     bool parameters,
     bool aligned,

@@ -24,6 +24,8 @@ _LIBRARY_PATH = Path(__file__).resolve().parent / "librln_sm100.so"
 _library = None
 
 _ptr = ctypes.c_void_p
+# RLN_BRANCH_FLOAT32 / FLOAT16 / BFLOAT16 of include/rln_sm100.h
+_BRANCH_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 
 def _load():
@@ -67,8 +69,8 @@ class HostPipeline:
     def __init__(self, hidden, branch_dtype=torch.float16, chunk_rows=8192, depth=3, device=None):
         if not torch.cuda.is_available():
             raise RuntimeError("HostPipeline needs a CUDA device; there is no CPU fallback")
-        if branch_dtype not in (torch.float16, torch.float32):
-            raise ValueError("branch must use float16 or float32")
+        if branch_dtype not in _BRANCH_CODES:
+            raise ValueError("branch must use float16, bfloat16 or float32")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
             else torch.device(device)
         self.hidden = int(hidden)
@@ -80,7 +82,7 @@ class HostPipeline:
             torch.cuda.current_stream()  # make sure the device's context exists
             status = _load().rln_sm100_host_pipeline_create(
                 ctypes.byref(self._handle), self.hidden,
-                int(branch_dtype == torch.float16), self.chunk_rows, self.depth,
+                _BRANCH_CODES[branch_dtype], self.chunk_rows, self.depth,
             )
         _check(status, "rln_sm100_host_pipeline_create")
 

@@ -12,6 +12,7 @@ Differences, all forced by the hardware change:
 
 * the capability gate asks for a CUDA device of compute capability 10.x and an
   importable ``_C`` extension instead of ROCm + gfx1010;
+* a bfloat16 branch is accepted in addition to float16 / float32;
 * ``implementation="triton"`` is always reported unavailable (there is no
   Triton route in this build);
 * in ``"auto"`` mode, eligible tensors on an sm_100 device never fall back to
@@ -34,6 +35,9 @@ MIN_HIDDEN_SIZE = 128
 MAX_HIDDEN_SIZE = 1024
 NATIVE_HIDDEN_SIZES = (128, 256, 384, 512, 768, 1024)
 NATIVE_COMPUTE_CAPABILITY_MAJOR = 10
+# float16 / float32 are the reference's branch types; bfloat16 is accepted in
+# addition (the sm_100a kernels have it, the gfx1010 ones could not).
+NATIVE_BRANCH_DTYPES = (torch.float16, torch.float32, torch.bfloat16)
 
 _IMPLEMENTATIONS = ("auto", "gfx1010", "triton", "torch")
 _NO_CUDA = "PyTorch CUDA/HIP is unavailable"
@@ -141,7 +145,7 @@ def _input_reason(x, branch, weight, bias, dropout_p, eps):
         return "weight and bias must match the final tensor dimension"
     if x.dtype != torch.float32:
         return "the optimized residual stream requires float32 x"
-    if branch.dtype not in (torch.float16, torch.float32):
+    if branch.dtype not in NATIVE_BRANCH_DTYPES:
         return "branch must use float16 or float32"
     if weight.dtype != torch.float32 or bias.dtype != torch.float32:
         return "weight and bias must use float32"

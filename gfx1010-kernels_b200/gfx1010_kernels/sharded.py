@@ -22,6 +22,10 @@ from typing import Callable, Optional, Tuple
 import torch
 
 
+# the extension's branch type codes: False/0 float32, True/1 float16, 2 bfloat16
+_BRANCH_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
 def shard_bounds(row_count: int, world_size: int, rank: int) -> Tuple[int, int]:
     """Rows ``[begin, end)`` of ``rank``: contiguous, ordered by rank, sizes differ by at most 1."""
     if world_size <= 0 or not 0 <= rank < world_size:
@@ -59,7 +63,7 @@ def _native_forward_backward(x, branch, weight, bias, grad_updated, grad_normali
     )
     grad_x, grad_branch, grad_weight, grad_bias = extension.residual_layer_norm_backward(
         grad_updated, grad_normalized, updated, weight, mean, rstd, mask,
-        float(dropout_p), bool(training), branch.dtype == torch.float16,
+        float(dropout_p), bool(training), _BRANCH_CODES[branch.dtype],
         128, 16, 64, 1, True,
     )
     # grad_weight / grad_bias are views of one [2, hidden] allocation

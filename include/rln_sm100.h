@@ -44,9 +44,20 @@ extern "C" {
 #define RLN_ERR_CUDA (-8)               /* a CUDA runtime call failed; see rln_sm100_last_cuda_error */
 #define RLN_ERR_HOST_BUFFERS (-9)       /* host-buffer pipeline: bad chunk size or context */
 #define RLN_ERR_LIMIT (-10)             /* size beyond a documented fixed maximum */
+#define RLN_ERR_BRANCH_DTYPE (-11)      /* branch_dtype is not one of RLN_BRANCH_* */
+
+/* Element type of `branch` / `grad_branch`.  0 and 1 are the reference's two
+ * cases (its entry points carry a bool "branch is half",
+ * csrc/residual_layer_norm.h:36); bfloat16 is an addition for mixed-precision
+ * training on this hardware.  Rounding rule for all three: the dropped branch
+ * is float32(b) * keep * scale rounded once to the branch type, grad_branch is
+ * the float32 gradient * keep * scale rounded once to the branch type. */
+#define RLN_BRANCH_FLOAT32 0
+#define RLN_BRANCH_FLOAT16 1
+#define RLN_BRANCH_BFLOAT16 2
 
 /* ABI version of this header; bumped on any signature change. */
-#define RLN_SM100_ABI_VERSION 2
+#define RLN_SM100_ABI_VERSION 3
 RLN_API int rln_sm100_abi_version(void);
 
 /* Human-readable text for a status code (static storage, never NULL). */
@@ -64,7 +75,7 @@ RLN_API int rln_sm100_last_cuda_error(void);
  * and the kernels it dispatches (forward kernel :425-545, vector4 kernel :353-422).
  *
  *   x            device, float32 [rows, hidden]
- *   branch       device, float16 (branch_is_half != 0) or float32, [rows, hidden]
+ *   branch       device, float32 / float16 / bfloat16 per branch_dtype (RLN_BRANCH_*), [rows, hidden]
  *   weight, bias device, float32 [hidden]
  *   updated      device out, float32 [rows, hidden]
  *   normalized   device out, float32 [rows, hidden]
@@ -83,7 +94,7 @@ RLN_API int rln_sm100_last_cuda_error(void);
  *                passes its global offset reproduces the mask of the unsharded
  *                call bit for bit.  0 for an unsharded call.
  *
- * Pointers that are 16-byte aligned (8-byte for a float16 branch) take the
+ * Pointers that are 16-byte aligned (8-byte for a 16-bit branch) take the
  * vectorised kernels; otherwise a scalar kernel with identical results in
  * exact arithmetic is used (the reference's alignment predicate :1084-1120).
  */
@@ -99,7 +110,7 @@ RLN_API int rln_sm100_forward(
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -134,7 +145,7 @@ RLN_API int rln_sm100_forward_device_rng(
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -172,7 +183,7 @@ RLN_API int64_t rln_sm100_backward_workspace_bytes(
  *   mean, rstd                               device, float32 [rows]
  *   dropout_mask     device, uint32 [rows*hidden/32] (ignored when dropout_active == 0)
  *   grad_x           device out, float32 [rows, hidden]
- *   grad_branch      device out, float16 or float32 [rows, hidden]
+ *   grad_branch      device out, [rows, hidden] in the branch type
  *   grad_parameters  device out, float32 [2, hidden]: row 0 = grad_weight
  *                    (sum over rows of grad_normalized * xhat), row 1 = grad_bias
  *                    (sum over rows of grad_normalized).  NULL = not requested
@@ -202,7 +213,7 @@ RLN_API int rln_sm100_backward(
     int64_t workspace_bytes,
     int64_t rows,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int32_t dropout_active,
     float dropout_p,
     int32_t deterministic,
@@ -256,7 +267,7 @@ RLN_API int rln_sm100_backward_static_scratch(
     float* grad_parameters,
     int64_t rows,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int32_t dropout_active,
     float dropout_p,
     void* stream);
@@ -296,7 +307,7 @@ typedef struct RlnHostPipeline RlnHostPipeline;
 RLN_API int rln_sm100_host_pipeline_create(
     RlnHostPipeline** pipeline,
     int32_t hidden,
-    int32_t branch_is_half,
+    int32_t branch_dtype,
     int64_t chunk_rows,
     int32_t depth);
 

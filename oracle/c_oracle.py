@@ -3,7 +3,7 @@
 Test infrastructure only.  The C code restates the reference kernels'
 arithmetic one element at a time; this module builds it on demand and exposes
 it on numpy arrays.  Half-precision branches are passed widened to float32 and
-come back as float32 values that are exactly representable in fp16.
+come back as float32 values that are exactly representable in the branch type.
 """
 
 import ctypes
@@ -45,7 +45,8 @@ def keep_mask(rows, hidden, dropout_p, seed, offset, row_base=0):
     return keep.astype(bool), words.view(np.int32)
 
 
-def forward(x, branch, weight, bias, keep, dropout_p, eps, branch_is_half):
+def forward(x, branch, weight, bias, keep, dropout_p, eps, branch_kind):
+    """``branch_kind``: 0/False float32, 1/True float16, 2 bfloat16."""
     x = np.ascontiguousarray(x, dtype=np.float32)
     rows, hidden = x.shape
     branch = np.ascontiguousarray(branch, dtype=np.float32)
@@ -59,7 +60,7 @@ def forward(x, branch, weight, bias, keep, dropout_p, eps, branch_is_half):
     _lib().rln_oracle_forward(
         _p(x), _p(branch), _p(weight), _p(bias),
         None if keep_bytes is None else _p(keep_bytes),
-        ctypes.c_float(dropout_p), ctypes.c_float(eps), ctypes.c_int32(int(branch_is_half)),
+        ctypes.c_float(dropout_p), ctypes.c_float(eps), ctypes.c_int32(int(branch_kind)),
         ctypes.c_int64(rows), ctypes.c_int32(hidden),
         _p(updated), _p(normalized), _p(mean), _p(rstd),
     )
@@ -67,7 +68,7 @@ def forward(x, branch, weight, bias, keep, dropout_p, eps, branch_is_half):
 
 
 def backward(grad_updated, grad_normalized, updated, weight, mean, rstd, keep, dropout_p,
-             branch_is_half):
+             branch_kind):
     updated = np.ascontiguousarray(updated, dtype=np.float32)
     rows, hidden = updated.shape
     grad_updated = np.ascontiguousarray(grad_updated, dtype=np.float32)
@@ -83,7 +84,7 @@ def backward(grad_updated, grad_normalized, updated, weight, mean, rstd, keep, d
     _lib().rln_oracle_backward(
         _p(grad_updated), _p(grad_normalized), _p(updated), _p(weight), _p(mean), _p(rstd),
         None if keep_bytes is None else _p(keep_bytes),
-        ctypes.c_float(dropout_p), ctypes.c_int32(int(branch_is_half)),
+        ctypes.c_float(dropout_p), ctypes.c_int32(int(branch_kind)),
         ctypes.c_int64(rows), ctypes.c_int32(hidden),
         _p(grad_x), _p(grad_branch), _p(grad_weight), _p(grad_bias),
     )

@@ -49,6 +49,26 @@ void rln_oracle_philox(const uint32_t counter_in[4], const uint32_t key[2], uint
 
 static float round_half(float v) { return (float)(_Float16)v; }
 
+/* float32 -> bfloat16 -> float32, round to nearest even (NaN kept quiet). */
+static float round_bfloat16(float v) {
+    union { float f; uint32_t u; } bits;
+    bits.f = v;
+    if ((bits.u & 0x7fffffffu) > 0x7f800000u) {
+        bits.u |= 0x00400000u;
+    } else {
+        bits.u += 0x7fffu + ((bits.u >> 16) & 1u);
+    }
+    bits.u &= 0xffff0000u;
+    return bits.f;
+}
+
+/* branch_kind: 0 float32 (no rounding), 1 float16, 2 bfloat16. */
+static float round_branch(float v, int32_t branch_kind) {
+    if (branch_kind == 1) return round_half(v);
+    if (branch_kind == 2) return round_bfloat16(v);
+    return v;
+}
+
 /* keep[rows * hidden] (0/1 bytes) and mask words [rows * hidden / 32]. */
 void rln_oracle_keep_mask(
     int64_t rows, int32_t hidden, float dropout_p, uint64_t seed, uint64_t offset,
@@ -72,11 +92,11 @@ void rln_oracle_keep_mask(
     }
 }
 
-/* branch is float32 values already widened; branch_is_half selects the rounding. */
+/* branch is float32 values already widened; branch_kind selects the rounding. */
 void rln_oracle_forward(
     const float* x, const float* branch, const float* weight, const float* bias,
     const uint8_t* keep /* NULL = dropout inactive */, float dropout_p, float eps,
-    int32_t branch_is_half, int64_t rows, int32_t hidden,
+    int32_t branch_kind, int64_t rows, int32_t hidden,
     float* updated, float* normalized, float* mean, float* rstd) {
     const float scale = keep ? 1.0f / (1.0f - dropout_p) : 1.0f;
     for (int64_t row = 0; row < rows; ++row) {
@@ -87,7 +107,7 @@ void rln_oracle_forward(
             if (keep) {
                 volatile float kept = b * (float)keep[base + c];   /* two un-fused products */
                 b = kept * scale;
-                if (branch_is_half) b = round_half(b);
+                b = round_branch(b, branch_kind);
             }
             volatile float u = x[base + c] + b;
             updated[base + c] = u;
@@ -113,7 +133,7 @@ void rln_oracle_backward(
     const float* grad_updated, const float* grad_normalized, const float* updated,
     const float* weight, const float* mean, const float* rstd,
     const uint8_t* keep /* NULL = dropout inactive */, float dropout_p,
-    int32_t branch_is_half, int64_t rows, int32_t hidden,
+    int32_t branch_kind, int64_t rows, int32_t hidden,
     float* grad_x, float* grad_branch /* widened to float32 */,
     float* grad_weight, float* grad_bias) {
     const float scale = keep ? 1.0f / (1.0f - dropout_p) : 1.0f;
@@ -144,7 +164,7 @@ void rln_oracle_backward(
                 volatile float kept = total * (float)keep[base + c];
                 b = kept * scale;
             }
-            grad_branch[base + c] = branch_is_half ? round_half(b) : b;
+            grad_branch[base + c] = round_branch(b, branch_kind);
         }
     }
     for (int32_t c = 0; c < hidden; ++c) {

@@ -21,6 +21,7 @@ _u64 = ctypes.c_uint64
 _f32 = ctypes.c_float
 
 _library = None
+BRANCH_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 
 def library():
@@ -79,7 +80,7 @@ def forward(x, branch, weight, bias, dropout_p, eps, training, seed=0, offset=0,
         _ptr(x), _ptr(branch), _ptr(weight), _ptr(bias),
         _ptr(updated), _ptr(normalized), _ptr(mean), _ptr(rstd),
         _ptr(mask) if active else None,
-        rows, hidden, int(branch.dtype == torch.float16), int(active),
+        rows, hidden, BRANCH_CODES[branch.dtype], int(active),
         dropout_p, eps, seed, offset, row_base, _stream(),
     )
     return status, updated, normalized, mean, rstd, mask
@@ -109,7 +110,7 @@ def backward(grad_updated, grad_normalized, updated, weight, mean, rstd, mask, d
         _ptr(grad_updated), _ptr(grad_normalized), _ptr(updated), _ptr(weight),
         _ptr(mean), _ptr(rstd), _ptr(mask) if active else None,
         _ptr(grad_x), _ptr(grad_branch), _ptr(grad_parameters), _ptr(workspace),
-        workspace_bytes, rows, hidden, int(branch_dtype == torch.float16), int(active),
+        workspace_bytes, rows, hidden, BRANCH_CODES[branch_dtype], int(active),
         dropout_p, int(deterministic), _stream(),
     )
     return status, grad_x, grad_branch, grad_parameters

@@ -63,6 +63,24 @@ def golden_cases():
     return cases
 
 
+def golden_tensors(case, device="cpu"):
+    """The arrays of one golden case as torch tensors, with ``branch`` and
+    ``grad_branch`` in the case's branch dtype (bfloat16 is stored widened to
+    float32, which represents it exactly)."""
+    import torch
+
+    dtype = getattr(torch, case["meta"]["branch_dtype"])
+    tensors = {}
+    for key, value in case.items():
+        if key in ("meta", "config"):
+            continue
+        tensor = torch.from_numpy(value)
+        if key in ("branch", "grad_branch"):
+            tensor = tensor.to(dtype)
+        tensors[key] = tensor.to(device)
+    return tensors
+
+
 @pytest.fixture(scope="session")
 def philox_kat():
     return json.loads((REPO / "tests" / "golden" / "philox_kat.json").read_text())

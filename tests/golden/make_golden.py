@@ -46,6 +46,9 @@ CASES = (
     ("h512_half_p0", (3,), 512, "float16", 0.0, 1e-3, True, 3, 0, 0),
     ("h768_half_p10", (2, 2), 768, "float16", 0.10, 1e-5, True, 4, 0xDEADBEEFCAFE, 4),
     ("h1024_float_p25", (3,), 1024, "float32", 0.25, 1e-5, True, 5, 7, 1 << 33),
+    # bfloat16 branch (an addition of the sm_100a build; the reference's own
+    # decomposition handles it through torch's type promotion)
+    ("h768_bfloat16_p10", (4,), 768, "bfloat16", 0.10, 1e-5, True, 6, 99, 12),
 )
 
 PHILOX_KAT = (
@@ -119,6 +122,8 @@ def main():
             "grad_weight": grads[2], "grad_bias": grads[3],
         }
         for key, tensor in record.items():
+            if tensor.dtype == torch.bfloat16:
+                tensor = tensor.float()  # numpy has no bfloat16; the values are exact in fp32
             arrays[f"{name}/{key}"] = tensor.numpy()
         arrays[f"{name}/mask"] = (
             rln_oracle.pack_mask(keep) if active else np.zeros(0, dtype=np.int32)

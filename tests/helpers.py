@@ -12,6 +12,17 @@ from oracle import rln_oracle
 NORMALIZED_TOL = dict(rtol=1e-5, atol=1e-6)      # vs the torch decomposition with the kernel's mask
 GRAD_X_TOL = dict(rtol=1e-5, atol=1e-5)
 GRAD_BRANCH_HALF_TOL = dict(rtol=2e-3, atol=1e-5)  # one fp16 rounding of an fp32-close value
+GRAD_BRANCH_BF16_TOL = dict(rtol=1.6e-2, atol=1e-5)  # one bfloat16 rounding (8 significant bits)
+
+
+def grad_branch_tolerance(branch_dtype):
+    import torch as _torch
+
+    if branch_dtype == _torch.float16:
+        return GRAD_BRANCH_HALF_TOL
+    if branch_dtype == _torch.bfloat16:
+        return GRAD_BRANCH_BF16_TOL
+    return GRAD_X_TOL
 PARAM_RTOL = 1e-4                                 # grad_weight / grad_bias, relative
 
 

@@ -8,7 +8,9 @@ import pytest
 from oracle import c_oracle, rln_oracle
 
 CASES = ["h128_half_p10", "h256_float_p15", "h384_half_eval", "h512_half_p0",
-         "h768_half_p10", "h1024_float_p25"]
+         "h768_half_p10", "h1024_float_p25", "h768_bfloat16_p10"]
+BRANCH_KIND = {"float32": 0, "float16": 1, "bfloat16": 2}
+ROUNDING = {"float32": 1e-5, "float16": 2e-3, "bfloat16": 1.6e-2}
 
 
 def test_c_philox_matches_known_answers(philox_kat):
@@ -30,7 +32,7 @@ def test_c_oracle_reproduces_reference_fixtures(golden_cases, name):
     case = golden_cases[name]
     meta = case["meta"]
     hidden = meta["hidden"]
-    half = case["branch"].dtype == np.float16
+    kind = BRANCH_KIND[meta["branch_dtype"]]
     x = case["x"].reshape(-1, hidden)
     rows = x.shape[0]
     active = meta["training"] and meta["dropout_p"] > 0
@@ -42,7 +44,7 @@ def test_c_oracle_reproduces_reference_fixtures(golden_cases, name):
         assert np.array_equal(words, case["mask"])
     updated, normalized, mean, rstd = c_oracle.forward(
         x, case["branch"].reshape(-1, hidden).astype(np.float32), case["weight"], case["bias"],
-        keep, meta["dropout_p"], meta["eps"], half,
+        keep, meta["dropout_p"], meta["eps"], kind,
     )
     assert np.array_equal(updated, case["updated"].reshape(-1, hidden))
     np.testing.assert_allclose(
@@ -52,12 +54,12 @@ def test_c_oracle_reproduces_reference_fixtures(golden_cases, name):
     np.testing.assert_allclose(rstd, case["rstd64"].reshape(-1), rtol=1e-5, atol=0)
     grad_x, grad_branch, grad_weight, grad_bias = c_oracle.backward(
         case["grad_updated"].reshape(-1, hidden), case["grad_normalized"].reshape(-1, hidden),
-        updated, case["weight"], mean, rstd, keep, meta["dropout_p"], half,
+        updated, case["weight"], mean, rstd, keep, meta["dropout_p"], kind,
     )
     np.testing.assert_allclose(grad_x, case["grad_x"].reshape(-1, hidden), rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(
         grad_branch, case["grad_branch"].reshape(-1, hidden).astype(np.float32),
-        rtol=2e-3 if half else 1e-5, atol=1e-5,
+        rtol=ROUNDING[meta["branch_dtype"]], atol=1e-5,
     )
     np.testing.assert_allclose(grad_weight, case["grad_weight"], rtol=1e-4, atol=1e-5)
     np.testing.assert_allclose(grad_bias, case["grad_bias"], rtol=1e-4, atol=1e-5)

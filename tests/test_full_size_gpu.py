@@ -23,7 +23,12 @@ import torch
 from torch.nn import functional as F
 
 import cabi
-from helpers import NORMALIZED_TOL, assert_parameters_close, unpack_mask_device
+from helpers import (
+    NORMALIZED_TOL,
+    assert_parameters_close,
+    grad_branch_tolerance,
+    unpack_mask_device,
+)
 
 pytestmark = pytest.mark.gpu
 
@@ -34,6 +39,7 @@ CONFIGS = {
     "transformer_width_768": (16 * 2048, 768, torch.float16, 0.1),
     "transformer_width_1024": (16 * 2048, 1024, torch.float16, 0.1),
     "headline_64Mi_h768": (87381, 768, torch.float16, 0.1),
+    "headline_64Mi_h768_bf16": (87381, 768, torch.bfloat16, 0.1),
     "ragged_h128_fp32": (3 * 1367, 128, torch.float32, 0.15),
     "ragged_h256_fp32": (5 * 817, 256, torch.float32, 0.15),
 }
@@ -97,7 +103,9 @@ def test_full_size_forward_and_backward_properties(name):
         assert torch.equal(a, b)                      # deterministic replay
     for a, b in zip(once[1:], doubled[1:]):
         expected = 2 * a.float()
-        if a.dtype == torch.float16:
+        if a.dtype == torch.bfloat16:
+            assert torch.equal(expected, b.float())       # bfloat16 has float32's exponent range
+        elif a.dtype == torch.float16:
             # doubling commutes with rounding except among fp16 subnormals,
             # where the grid spacing (2**-24) does not scale with the value
             normal = a.float().abs() >= 2.0 ** -13
@@ -129,10 +137,8 @@ def test_full_size_forward_and_backward_properties(name):
         (reference_updated, reference_normalized), leaves, (grad_updated, grad_normalized)
     )
     torch.testing.assert_close(grad_x, reference[0], rtol=1e-5, atol=1e-5)
-    half = branch_dtype == torch.float16
     torch.testing.assert_close(
-        grad_branch.float(), reference[1].float(),
-        rtol=2e-3 if half else 1e-5, atol=1e-5,
+        grad_branch.float(), reference[1].float(), **grad_branch_tolerance(branch_dtype)
     )
     assert_parameters_close(grad_parameters[0], reference[2], rows, "grad_weight vs autograd")
     assert_parameters_close(grad_parameters[1], reference[3], rows, "grad_bias vs autograd")

@@ -202,7 +202,8 @@ def test_input_reason_ladder_with_fake_device_tensors():
     assert "divisible by 8" in reason(Fake((4, 132)))
     assert "final tensor dimension" in reason(ok, weight=Fake((128,)))
     assert "float32 x" in reason(Fake((4, 256), dtype=torch.float16))
-    assert "float16 or float32" in reason(ok, branch=Fake((4, 256), dtype=torch.bfloat16))
+    assert "float16 or float32" in reason(ok, branch=Fake((4, 256), dtype=torch.float64))
+    assert reason(ok, branch=Fake((4, 256), dtype=torch.bfloat16)) is None
     assert "weight and bias must use float32" in reason(ok, bias=Fake((256,), dtype=torch.float16))
     assert "contiguous" in reason(ok, branch=Fake((4, 256), contiguous=False))
     assert "dropout_p must be in [0, 1)" in reason(ok, p=1.0)

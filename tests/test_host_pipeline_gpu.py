@@ -20,6 +20,7 @@ pytestmark = pytest.mark.gpu
         (257, 128, torch.float32, 100, 2, True),
         (64, 1024, torch.float16, 4096, 2, False),   # single partial chunk
         (4101, 256, torch.float32, 512, 4, False),
+        (777, 512, torch.bfloat16, 256, 3, True),
     ],
 )
 def test_host_pipeline_matches_device_calls(rows, hidden, branch_dtype, chunk_rows, depth,

@@ -12,9 +12,10 @@ import pytest
 import torch
 
 import cabi
+from conftest import golden_tensors
 from helpers import (
-    GRAD_BRANCH_HALF_TOL,
     GRAD_X_TOL,
+    grad_branch_tolerance,
     NORMALIZED_TOL,
     assert_parameters_close,
     draw_inputs,
@@ -68,8 +69,9 @@ def run_and_check(shape, hidden, branch_dtype, dropout_p, seed, *, training=True
     torch.cuda.synchronize()
     torch.testing.assert_close(grad_x, expected[2], **GRAD_X_TOL)
     torch.testing.assert_close(grad_x.double(), arbiter[2].double(), **GRAD_X_TOL)
-    branch_tol = GRAD_BRANCH_HALF_TOL if branch_dtype == torch.float16 else GRAD_X_TOL
-    torch.testing.assert_close(grad_branch.float(), expected[3].float(), **branch_tol)
+    torch.testing.assert_close(
+        grad_branch.float(), expected[3].float(), **grad_branch_tolerance(branch_dtype)
+    )
     assert_parameters_close(grad_parameters[0], arbiter[4], rows, "grad_weight")
     assert_parameters_close(grad_parameters[1], arbiter[5], rows, "grad_bias")
     return dict(
@@ -81,7 +83,9 @@ def run_and_check(shape, hidden, branch_dtype, dropout_p, seed, *, training=True
 
 
 @pytest.mark.parametrize("hidden", HIDDEN_SIZES)
-@pytest.mark.parametrize("branch_dtype", [torch.float16, torch.float32], ids=["half", "float"])
+@pytest.mark.parametrize(
+    "branch_dtype", [torch.float16, torch.float32, torch.bfloat16], ids=["half", "float", "bf16"]
+)
 @pytest.mark.parametrize("dropout_p", [0.0, 0.1])
 def test_forward_backward_parity_all_widths(hidden, branch_dtype, dropout_p):
     run_and_check((1, 37), hidden, branch_dtype, dropout_p, seed=17 + hidden,
@@ -144,12 +148,12 @@ def test_large_eps_and_nearly_constant_rows():
 @pytest.mark.parametrize(
     "name",
     ["h128_half_p10", "h256_float_p15", "h384_half_eval", "h512_half_p0", "h768_half_p10",
-     "h1024_float_p25"],
+     "h1024_float_p25", "h768_bfloat16_p10"],
 )
 def test_golden_fixtures_from_the_reference(golden_cases, name):
     case = golden_cases[name]
     meta = case["meta"]
-    t = {k: torch.from_numpy(v).cuda() for k, v in case.items() if k not in ("meta", "config")}
+    t = golden_tensors(case, device="cuda")
     hidden = meta["hidden"]
     branch_dtype = t["branch"].dtype
     status, updated, normalized, mean, rstd, mask = cabi.forward(
@@ -172,8 +176,9 @@ def test_golden_fixtures_from_the_reference(golden_cases, name):
         )
         assert status == 0, cabi.status_text(status)
         torch.testing.assert_close(grad_x, t["grad_x"], **GRAD_X_TOL)
-        tol = GRAD_BRANCH_HALF_TOL if branch_dtype == torch.float16 else GRAD_X_TOL
-        torch.testing.assert_close(grad_branch.float(), t["grad_branch"].float(), **tol)
+        torch.testing.assert_close(
+            grad_branch.float(), t["grad_branch"].float(), **grad_branch_tolerance(branch_dtype)
+        )
         assert_parameters_close(grad_parameters[0], t["grad_weight"], rows, "grad_weight")
         assert_parameters_close(grad_parameters[1], t["grad_bias"], rows, "grad_bias")
 
@@ -286,7 +291,9 @@ def test_updated_only_gradient_passes_through_exactly():
 
 
 @pytest.mark.parametrize("hidden", [128, 384, 1024])
-@pytest.mark.parametrize("branch_dtype", [torch.float16, torch.float32], ids=["half", "float"])
+@pytest.mark.parametrize(
+    "branch_dtype", [torch.float16, torch.float32, torch.bfloat16], ids=["half", "float", "bf16"]
+)
 def test_misaligned_pointers_take_the_scalar_kernels_with_identical_results(hidden, branch_dtype):
     rows = 23
     x, branch, weight, bias, grad_updated, grad_normalized = draw_inputs(
@@ -369,7 +376,8 @@ def test_c_abi_rejects_bad_arguments_on_device():
 
 
 @pytest.mark.parametrize("hidden,branch_dtype", [(128, torch.float32), (768, torch.float16),
-                                                 (1024, torch.float16)])
+                                                 (1024, torch.float16), (256, torch.bfloat16),
+                                                 (768, torch.bfloat16)])
 def test_cuda_path_matches_the_scalar_c_oracle(hidden, branch_dtype):
     """Independent second oracle: ``oracle/rln_oracle.c`` walks the reference
     kernels' formulas one element at a time."""
@@ -379,7 +387,7 @@ def test_cuda_path_matches_the_scalar_c_oracle(hidden, branch_dtype):
     x, branch, weight, bias, grad_updated, grad_normalized = draw_inputs(
         (rows,), hidden, branch_dtype, 31
     )
-    half = branch_dtype == torch.float16
+    half = cabi.BRANCH_CODES[branch_dtype]   # the C oracle's branch kind
     status, updated, normalized, mean, rstd, mask = cabi.forward(
         x, branch, weight, bias, p, eps, True, seed=seed, offset=offset, row_base=row_base
     )
@@ -405,7 +413,8 @@ def test_cuda_path_matches_the_scalar_c_oracle(hidden, branch_dtype):
     )
     np.testing.assert_allclose(grad_x.cpu().numpy(), reference[0], rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(
-        grad_branch.float().cpu().numpy(), reference[1], rtol=2e-3 if half else 1e-5, atol=1e-5
+        grad_branch.float().cpu().numpy(), reference[1],
+        rtol=grad_branch_tolerance(branch_dtype)["rtol"], atol=1e-5,
     )
     np.testing.assert_allclose(grad_parameters[0].cpu().numpy(), reference[2], rtol=1e-4, atol=5e-5)
     np.testing.assert_allclose(grad_parameters[1].cpu().numpy(), reference[3], rtol=1e-4, atol=5e-5)

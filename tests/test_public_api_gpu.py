@@ -531,3 +531,36 @@ def test_work_is_enqueued_on_the_current_stream():
     side.synchronize()
     expected = decomposition(*inputs)
     torch.testing.assert_close(actual[1], expected[1], rtol=1e-5, atol=1e-6)
+
+
+def test_bfloat16_branch_forward_and_backward():
+    """bfloat16 is accepted in addition to the reference's float16 / float32."""
+    torch.manual_seed(251)
+    data = random_inputs(37, 768, branch_dtype=torch.bfloat16)
+    assert can_use_residual_layer_norm(*data)
+    actual_inputs = leaves(data)
+    expected_inputs = leaves(data)
+    actual = residual_layer_norm(*actual_inputs, implementation="gfx1010")
+    expected = decomposition(*expected_inputs)
+    grad_updated = torch.randn_like(actual[0])
+    grad_normalized = torch.randn_like(actual[1])
+    actual_gradients = torch.autograd.grad(actual, actual_inputs, (grad_updated, grad_normalized))
+    expected_gradients = torch.autograd.grad(
+        expected, expected_inputs, (grad_updated, grad_normalized)
+    )
+    torch.testing.assert_close(actual[0], expected[0], rtol=0, atol=0)
+    torch.testing.assert_close(actual[1], expected[1], rtol=1e-5, atol=1e-6)
+    assert actual_gradients[1].dtype == torch.bfloat16
+    torch.testing.assert_close(actual_gradients[0], expected_gradients[0], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(
+        actual_gradients[1].float(), expected_gradients[1].float(), rtol=1.6e-2, atol=1e-5
+    )
+    for mine, theirs in zip(actual_gradients[2:], expected_gradients[2:]):
+        torch.testing.assert_close(mine, theirs, rtol=1e-4, atol=2e-4)
+    # dropout on a unit branch: updated - x is 0 or bfloat16(1 / (1 - p))
+    ones = torch.ones(64, 768, device=DEVICE, dtype=torch.bfloat16)
+    zeros = torch.zeros(64, 768, device=DEVICE)
+    updated = residual_layer_norm(zeros, ones, data[2], data[3], dropout_p=0.3,
+                                  implementation="gfx1010")[0]
+    kept_value = torch.tensor(1.0 / (1.0 - 0.3), dtype=torch.float32).to(torch.bfloat16).float()
+    assert set(updated.unique().tolist()) <= {0.0, kept_value.item()}

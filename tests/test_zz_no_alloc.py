@@ -60,7 +60,7 @@ def _static_backward(grad_updated, grad_normalized, updated, weight, mean, rstd,
         weight.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
         mask.data_ptr() if active else None,
         grad_x.data_ptr(), grad_branch.data_ptr(), grad_parameters.data_ptr(),
-        rows, hidden, int(branch_dtype == torch.float16), int(active), dropout_p,
+        rows, hidden, cabi.BRANCH_CODES[branch_dtype], int(active), dropout_p,
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
     )
     return status, grad_x, grad_branch, grad_parameters
@@ -78,7 +78,7 @@ def _case(rows, hidden, branch_dtype, dropout_p, seed):
 
 
 @pytest.mark.parametrize("hidden,branch_dtype", [(768, torch.float16), (128, torch.float32),
-                                                 (1024, torch.float16)])
+                                                 (1024, torch.float16), (384, torch.bfloat16)])
 def test_static_scratch_backward_matches_workspace_backward_twice_in_a_row(hidden, branch_dtype):
     dropout_p = 0.1
     # first call fills the whole persistent grid, second call uses a few CTAs only
