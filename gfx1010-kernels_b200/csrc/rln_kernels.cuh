@@ -210,11 +210,13 @@ __device__ __forceinline__ void stream_store(uint2* p, uint2 v) {
 #endif
 }
 
-// kStream selects the streaming cache hints above.  Measured on B200: the
-// backward gains ~4 % from them.  The forward alone, in short bursts, is
-// ~1.5 % faster with plain accesses, but inside a sustained forward+backward
-// chain (power-capped clocks) the hints are 0.25 % ahead, so both kernels use
-// them; the forward kernels keep the choice as a template parameter.
+// kStream selects the streaming cache hints above.  Both kernels take the
+// choice as a template parameter (kStreamHints) and ship with plain accesses:
+// timed alone in short bursts the backward is ~4 % faster with the hints, but
+// in a sustained forward+backward chain on random data (the board at its power
+// cap, which is how the operator runs in training) plain accesses in both
+// kernels are 2 % faster per step than hints in both, and mixed settings lie
+// in between.
 template <bool kAligned, bool kStream = true>
 __device__ __forceinline__ float4 load_f4(const float* base, int64_t chunk) {
     if constexpr (kAligned) {
@@ -275,9 +277,9 @@ struct BranchIO<float> {
     static __device__ __forceinline__ float4 load(const void* base, int64_t chunk) {
         return load_f4<kAligned, kStream>(static_cast<const float*>(base), chunk);
     }
-    template <bool kAligned>
+    template <bool kAligned, bool kStream = true>
     static __device__ __forceinline__ void store(void* base, int64_t chunk, float4 v) {
-        store_f4<kAligned>(static_cast<float*>(base), chunk, v);
+        store_f4<kAligned, kStream>(static_cast<float*>(base), chunk, v);
     }
     static __device__ __forceinline__ float round(float v) { return v; }
 };
@@ -298,7 +300,7 @@ struct BranchIO<__half> {
                 __half2float(p[0]), __half2float(p[1]), __half2float(p[2]), __half2float(p[3]));
         }
     }
-    template <bool kAligned>
+    template <bool kAligned, bool kStream = true>
     static __device__ __forceinline__ void store(void* base, int64_t chunk, float4 v) {
         if constexpr (kAligned) {
             const __half2 lo = __floats2half2_rn(v.x, v.y);
@@ -306,7 +308,11 @@ struct BranchIO<__half> {
             uint2 raw;
             raw.x = *reinterpret_cast<const uint32_t*>(&lo);
             raw.y = *reinterpret_cast<const uint32_t*>(&hi);
-            stream_store(static_cast<uint2*>(base) + chunk, raw);
+            if constexpr (kStream) {
+                stream_store(static_cast<uint2*>(base) + chunk, raw);
+            } else {
+                *(static_cast<uint2*>(base) + chunk) = raw;
+            }
         } else {
             __half* p = static_cast<__half*>(base) + chunk * 4;
             p[0] = __float2half_rn(v.x);
@@ -343,7 +349,7 @@ struct BranchIO<__nv_bfloat16> {
                 __bfloat162float(p[3]));
         }
     }
-    template <bool kAligned>
+    template <bool kAligned, bool kStream = true>
     static __device__ __forceinline__ void store(void* base, int64_t chunk, float4 v) {
         if constexpr (kAligned) {
             const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
@@ -351,7 +357,11 @@ struct BranchIO<__nv_bfloat16> {
             uint2 raw;
             raw.x = *reinterpret_cast<const uint32_t*>(&lo);
             raw.y = *reinterpret_cast<const uint32_t*>(&hi);
-            stream_store(static_cast<uint2*>(base) + chunk, raw);
+            if constexpr (kStream) {
+                stream_store(static_cast<uint2*>(base) + chunk, raw);
+            } else {
+                *(static_cast<uint2*>(base) + chunk) = raw;
+            }
         } else {
             __nv_bfloat16* p = static_cast<__nv_bfloat16*>(base) + chunk * 4;
             p[0] = __float2bfloat16_rn(v.x);
@@ -387,7 +397,7 @@ __device__ __forceinline__ float drop_one(float b, bool keep, float scale) {
 // Forward.  grid-stride over groups of kRows consecutive rows per warp.
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kRows,
-          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = true>
+          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = false>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_kernel(const ForwardParams p) {
     static_assert(H % 128 == 0, "hidden must be a multiple of 128");
@@ -542,7 +552,7 @@ rln_forward_kernel(const ForwardParams p) {
 // stores are predicated, shuffles are executed by the whole warp.
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kLanes,
-          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = true>
+          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = false>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_subwarp_kernel(const ForwardParams p) {
     static_assert(kLanes == 8 || kLanes == 16, "a row is owned by 8 or 16 lanes");
@@ -698,7 +708,7 @@ __device__ __forceinline__ void red_add_f4(float* address, float4 v) {
 }
 
 template <int H, typename BranchT, bool kDropout, bool kParams, bool kAligned, int kWarps, int kRows,
-          int kMinCtas = 1>
+          int kMinCtas = 1, bool kStreamHints = false>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_backward_kernel(const BackwardParams p) {
     static_assert(H % 128 == 0, "hidden must be a multiple of 128");
@@ -742,9 +752,9 @@ rln_backward_kernel(const BackwardParams p) {
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
                     const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
-                    gy[r][k] = load_f4<kAligned>(p.grad_normalized, chunk);
-                    uu[r][k] = load_f4<kAligned>(p.updated, chunk);
-                    gu[r][k] = load_f4<kAligned>(p.grad_updated, chunk);
+                    gy[r][k] = load_f4<kAligned, kStreamHints>(p.grad_normalized, chunk);
+                    uu[r][k] = load_f4<kAligned, kStreamHints>(p.updated, chunk);
+                    gu[r][k] = load_f4<kAligned, kStreamHints>(p.grad_updated, chunk);
                     if constexpr (kDropout) {
                         words[r][k] = __ldg(p.mask + row * kWordsPerRow + 4 * k + (lane >> 3));
                     }
@@ -806,7 +816,7 @@ rln_backward_kernel(const BackwardParams p) {
                 total.y = gu[r][k].y + rs * (gy[r][k].y - mean_q - uu[r][k].y * mean_qx);
                 total.z = gu[r][k].z + rs * (gy[r][k].z - mean_q - uu[r][k].z * mean_qx);
                 total.w = gu[r][k].w + rs * (gy[r][k].w - mean_q - uu[r][k].w * mean_qx);
-                store_f4<kAligned>(p.grad_x, chunk, total);
+                store_f4<kAligned, kStreamHints>(p.grad_x, chunk, total);
                 if constexpr (kDropout) {
                     const uint32_t n = words[r][k] >> (4 * (lane & 7));
                     total.x = __fmul_rn(__fmul_rn(total.x, (n & 1u) ? 1.0f : 0.0f), p.scale);
@@ -814,7 +824,7 @@ rln_backward_kernel(const BackwardParams p) {
                     total.z = __fmul_rn(__fmul_rn(total.z, (n & 4u) ? 1.0f : 0.0f), p.scale);
                     total.w = __fmul_rn(__fmul_rn(total.w, (n & 8u) ? 1.0f : 0.0f), p.scale);
                 }
-                IO::template store<kAligned>(p.grad_branch, chunk, total);
+                IO::template store<kAligned, kStreamHints>(p.grad_branch, chunk, total);
             }
         }
     }
