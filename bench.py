@@ -64,7 +64,7 @@ WORKLOADS = {
 }
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch,
 # taken from an ncu capture of that workload (two launches, --set full), per workload.
-NCU_BACKWARD_TRAFFIC_BYTES = {"h768_64Mi": 814_416_128 + 351_629_824}
+NCU_BACKWARD_TRAFFIC_BYTES = {"h768_64Mi": 814_518_016 + 363_732_992}
 # the extension's branch type codes (False/0 float32, True/1 float16, 2 bfloat16)
 BRANCH_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 CPU_SAMPLE_ROWS = 8192
