@@ -146,11 +146,12 @@ __device__ __forceinline__ PhiloxState resolve_philox_state(const ForwardParams&
 }
 
 // ---------------------------------------------------------------------------
-// Global-memory access.  Row data is touched once, so it is streamed
-// (evict-first); kAligned == false is the 4-byte-aligned fallback with the
-// same lane->column mapping and therefore bit-identical arithmetic.
+// Global-memory access.  kAligned == false is the 4-byte-aligned fallback with
+// the same lane->column mapping and therefore bit-identical arithmetic.  Row
+// data is touched once; streaming cache hints are available as an option (see
+// kStream below) but are not what ships.
 // ---------------------------------------------------------------------------
-// Cache policy of the streamed accesses (compile-time tunables).
+// Cache policy of the hinted accesses (compile-time tunables, used when kStream is on).
 //   RLN_LOAD_POLICY : 0 plain, 1 ld.global.nc (__ldg), 2 evict-first (__ldcs),
 //                     3 ld.global.nc.L1::no_allocate
 //   RLN_STORE_POLICY: 0 plain, 1 evict-first (__stcs), 2 write-through (__stwt)
