@@ -14,10 +14,10 @@ namespace rln {
 //   kWarps    warps per CTA;
 //   kRows     consecutive rows a warp keeps in flight per loop iteration;
 //   kMinCtas  __launch_bounds__ minimum, i.e. the register budget
-//             65536 / (32 * kWarps * kMinCtas) per thread.  About 16 resident
-//             warps per SM (more for narrow rows) is the sweet spot for the
-//             forward: fewer warps leave HBM latency exposed, more warps cut
-//             the registers a warp can keep in flight;
+//             65536 / (32 * kWarps * kMinCtas) per thread.  16 to 32 resident
+//             warps per SM is the sweet spot for the forward: fewer warps leave
+//             HBM latency exposed, more warps cut the registers a warp can keep
+//             in flight;
 //   kPersistent (forward) launch exactly sm_count * kMinCtas CTAs that
 //             grid-stride, instead of one CTA per kWarps * kRows rows.  Not
 //             used by the current table: with several rows per warp even the
@@ -29,10 +29,16 @@ struct ForwardTune {
     // for the two narrowest widths (H=128: +14 %, H=256: +1 %) and loses from
     // H=384 up.
     static constexpr int kLanes = H <= 128 ? 8 : (H <= 256 ? 16 : 32);
-    static constexpr int kWarps = 4;
+    // The forward has no CTA-wide step at all, so the CTA is only a scheduling
+    // unit.  For wide rows the smallest unit wins in a sustained
+    // forward+backward chain on random data: a one-warp CTA frees its slot the
+    // moment its row is stored instead of waiting for the slowest of four
+    // warps (step time, same board: H=1024 -3.4 %, H=768 -3.1 % against
+    // 4 warps x 4 / 5 CTAs; H=512 and 384 gain about 1 % with two warps).
+    static constexpr int kWarps = H <= 256 ? 4 : (H <= 512 ? 2 : 1);
     static constexpr int kRows = 1;
     static constexpr int kMinCtas =
-        H <= 256 ? 6 : (H <= 384 ? 8 : (H <= 512 ? 6 : (H <= 768 ? 5 : 4)));
+        H <= 256 ? 6 : (H <= 384 ? 16 : (H <= 512 ? 12 : (H <= 768 ? 18 : 16)));
     static constexpr bool kPersistent = false;
 };
 
