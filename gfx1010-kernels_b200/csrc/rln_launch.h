@@ -52,7 +52,9 @@ struct BackwardTune {
     // Chosen in a sustained forward+backward chain on random data (the board at
     // its power cap); short bursts of the backward alone rank some neighbours
     // differently by 1-2 %.
-    static constexpr int kWarps = 4;
+    // H=1024: three warps x two CTAs (six warps per SM, up to 255 registers
+    // each) beat four warps x two by 2 % of the step.
+    static constexpr int kWarps = H == 1024 ? 3 : 4;
     static constexpr int kRows = H == 128 ? 2 : 1;
     static constexpr int kCtasPerSm =
         H <= 128 ? 6 : (H <= 256 ? 5 : (H <= 512 ? 4 : 2));
