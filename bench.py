@@ -61,25 +61,40 @@ WORKLOADS = {
     "h768_64Mi_bf16_branch": (87381, 768, torch.bfloat16, 0.1),
     "h128_64Mi": (524288, 128, torch.float16, 0.1),
     "h256_64Mi": (262144, 256, torch.float16, 0.1),
+    # `normalized` (and its gradient) in bfloat16: a fifth field, float32 when absent
+    "h768_64Mi_bf16_normalized": (87381, 768, torch.float16, 0.1, torch.bfloat16),
+    "h768_64Mi_bf16_branch_bf16_normalized": (87381, 768, torch.bfloat16, 0.1, torch.bfloat16),
+    "c5_64x4096x1024_bf16_normalized": (262144, 1024, torch.float16, 0.1, torch.bfloat16),
 }
+
+
+def workload(name):
+    """(rows per GPU, hidden, branch dtype, dropout p, normalized dtype)."""
+    fields = WORKLOADS[name]
+    return (*fields[:4], fields[4] if len(fields) > 4 else torch.float32)
+
+
+
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch,
 # taken from an ncu capture of that workload (two launches, --set full), per workload.
 NCU_BACKWARD_TRAFFIC_BYTES = {"h768_64Mi": 814_518_016 + 363_732_992}
-# the extension's branch type codes (False/0 float32, True/1 float16, 2 bfloat16)
+# the extension's element type codes (False/0 float32, True/1 float16, 2 bfloat16)
 BRANCH_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+NORMALIZED_CODES = BRANCH_CODES
 CPU_SAMPLE_ROWS = 8192
 EPS = 1e-5
 
 
-def forward_bytes_per_row(hidden, branch_bytes, dropout):
-    """read x 4H + branch sb*H; write updated 4H + normalized 4H + mean 4 + rstd 4 (+ mask H/8)."""
-    return (12 + branch_bytes) * hidden + 8 + (hidden // 8 if dropout else 0)
+def forward_bytes_per_row(hidden, branch_bytes, dropout, normalized_bytes=4):
+    """read x 4H + branch sb*H; write updated 4H + normalized sn*H + mean 4 + rstd 4
+    (+ mask H/8)."""
+    return (8 + branch_bytes + normalized_bytes) * hidden + 8 + (hidden // 8 if dropout else 0)
 
 
-def backward_bytes_per_row(hidden, branch_bytes, dropout):
-    """read grad_updated, grad_normalized, updated 12H + mean 4 + rstd 4 (+ mask H/8);
+def backward_bytes_per_row(hidden, branch_bytes, dropout, normalized_bytes=4):
+    """read grad_updated 4H, grad_normalized sn*H, updated 4H + mean 4 + rstd 4 (+ mask H/8);
     write grad_x 4H + grad_branch sb*H."""
-    return (16 + branch_bytes) * hidden + 8 + (hidden // 8 if dropout else 0)
+    return (12 + branch_bytes + normalized_bytes) * hidden + 8 + (hidden // 8 if dropout else 0)
 
 
 def measured_peak_gbs():
@@ -200,7 +215,8 @@ class ClockSampler:
         }
 
 
-def time_cpu_reference(rows, hidden, branch_dtype, dropout_p, steps, warmup):
+def time_cpu_reference(rows, hidden, branch_dtype, dropout_p, steps, warmup,
+                       normalized_dtype=torch.float32):
     """The reference's CPU path: its torch decomposition (F.dropout -> add ->
     F.layer_norm) forward plus torch.autograd.grad, on all host threads."""
     from oracle import rln_oracle
@@ -211,10 +227,13 @@ def time_cpu_reference(rows, hidden, branch_dtype, dropout_p, steps, warmup):
         rows, hidden, branch_dtype, seed=0
     )
     leaves = [t.requires_grad_(True) for t in (x, branch, weight, bias)]
+    grad_normalized = grad_normalized.to(normalized_dtype)
     times = []
     for index in range(warmup + steps):
         begin = time.perf_counter()
-        outputs = rln_oracle.torch_decomposition(*leaves, dropout_p, EPS, True, None)
+        outputs = rln_oracle.torch_decomposition(
+            *leaves, dropout_p, EPS, True, None, normalized_dtype
+        )
         torch.autograd.grad(outputs, leaves, (grad_updated, grad_normalized))
         elapsed = time.perf_counter() - begin
         if index >= warmup:
@@ -225,9 +244,11 @@ def time_cpu_reference(rows, hidden, branch_dtype, dropout_p, steps, warmup):
 def run_reference_arm(args, rank):
     if rank != 0:
         return 0
-    rows_full, hidden, branch_dtype, dropout_p = WORKLOADS[args.workload]
+    rows_full, hidden, branch_dtype, dropout_p, normalized_dtype = workload(args.workload)
     rows = min(rows_full, CPU_SAMPLE_ROWS)
-    times, threads = time_cpu_reference(rows, hidden, branch_dtype, dropout_p, args.steps, args.warmup)
+    times, threads = time_cpu_reference(
+        rows, hidden, branch_dtype, dropout_p, args.steps, args.warmup, normalized_dtype
+    )
     total = sum(times)
     value = rows * len(times) / total
     sample = (
@@ -260,7 +281,7 @@ def run_reference_arm(args, rank):
 
 
 def workload_config(name, gpus):
-    rows, hidden, branch_dtype, dropout_p = WORKLOADS[name]
+    rows, hidden, branch_dtype, dropout_p, normalized_dtype = workload(name)
     return {
         "workload": name,
         "rows_per_gpu": rows,
@@ -268,6 +289,7 @@ def workload_config(name, gpus):
         "hidden": hidden,
         "x_dtype": "float32",
         "branch_dtype": str(branch_dtype).split(".")[-1],
+        "normalized_dtype": str(normalized_dtype).split(".")[-1],
         "dropout_p": dropout_p,
         "eps": EPS,
         "training": True,
@@ -300,10 +322,14 @@ def run_native_arm(args, rank, local_rank, world):
             "nccl", device_id=device, timeout=datetime.timedelta(seconds=120)
         )
 
-    rows, hidden, branch_dtype, dropout_p = WORKLOADS[args.workload]
+    rows, hidden, branch_dtype, dropout_p, normalized_dtype = workload(args.workload)
     branch_bytes = 4 if branch_dtype == torch.float32 else 2
+    normalized_bytes = 4 if normalized_dtype == torch.float32 else 2
+    # the host-buffer pipeline moves a float32 `normalized`: no end-to-end leg otherwise
+    skip_e2e = args.kernel_only or normalized_dtype != torch.float32
     host = draw_inputs(rows, hidden, branch_dtype, seed=rank)
     x, branch, weight, bias, grad_updated, grad_normalized = (t.to(device) for t in host)
+    grad_normalized = grad_normalized.to(normalized_dtype)
     if world > 1:
         # replicated parameters: every rank uses rank 0's values
         dist.broadcast(weight, 0)
@@ -337,7 +363,8 @@ def run_native_arm(args, rank, local_rank, world):
             e2 = torch.cuda.Event(enable_timing=True)
             e0.record()
         updated, normalized, mean, rstd, mask = _C.residual_layer_norm_forward_seeded(
-            x, branch, weight, bias, dropout_p, EPS, True, 128, seed, 4 * index, row_base
+            x, branch, weight, bias, dropout_p, EPS, True, 128, seed, 4 * index, row_base,
+            NORMALIZED_CODES[normalized_dtype],
         )
         # The backward is a persistent grid that fills every SM exactly once; a
         # communication kernel still resident from the previous step would push
@@ -442,7 +469,7 @@ def run_native_arm(args, rank, local_rank, world):
         clocks["window"] = "warm-up + timed region (timed region shorter than the sampling interval)"
 
     # end-to-end: pinned host inputs -> device -> public API fwd+bwd -> results back to host
-    if args.kernel_only:
+    if skip_e2e:
         e2e = {"ms": float("nan"), "public_ms": float("nan"), "steps": 0, "h2d": 0, "d2h": 0}
     else:
         e2e = run_end_to_end(
@@ -465,15 +492,19 @@ def run_native_arm(args, rank, local_rank, world):
         peak, peak_kind = measured_peak_gbs()
         total_rows = rows * world
         value = total_rows * args.steps / (elapsed_ms * 1e-3)
-        fwd_bytes = forward_bytes_per_row(hidden, branch_bytes, dropout_p > 0) * rows
-        bwd_bytes = backward_bytes_per_row(hidden, branch_bytes, dropout_p > 0) * rows
+        fwd_row = forward_bytes_per_row(hidden, branch_bytes, dropout_p > 0, normalized_bytes)
+        bwd_row = backward_bytes_per_row(hidden, branch_bytes, dropout_p > 0, normalized_bytes)
+        fwd_bytes = fwd_row * rows
+        bwd_bytes = bwd_row * rows
         fwd_gbs = fwd_bytes / (forward_ms * 1e-3) / 1e9
         bwd_gbs = bwd_bytes / (backward_ms * 1e-3) / 1e9
         step_gbs = (fwd_bytes + bwd_bytes) * world * args.steps / (elapsed_ms * 1e-3) / 1e9
         cpu = None
         if world == 1 and not args.kernel_only:
             sample_rows = min(rows, CPU_SAMPLE_ROWS)
-            times, threads = time_cpu_reference(sample_rows, hidden, branch_dtype, dropout_p, 5, 1)
+            times, threads = time_cpu_reference(
+                sample_rows, hidden, branch_dtype, dropout_p, 5, 1, normalized_dtype
+            )
             cpu = {
                 "value": sample_rows / statistics.median(times),
                 "unit": UNIT,
@@ -501,10 +532,8 @@ def run_native_arm(args, rank, local_rank, world):
             "hbm_frac_of_8000": step_gbs / (HBM_SPEC_GBS * world),
             "hbm_frac_of_measured": step_gbs / (peak * world),
             "kernels": {
-                "forward": {"ms": forward_ms, "gbs": fwd_gbs, "bytes_per_row":
-                            forward_bytes_per_row(hidden, branch_bytes, dropout_p > 0)},
-                "backward": {"ms": backward_ms, "gbs": bwd_gbs, "bytes_per_row":
-                             backward_bytes_per_row(hidden, branch_bytes, dropout_p > 0)},
+                "forward": {"ms": forward_ms, "gbs": fwd_gbs, "bytes_per_row": fwd_row},
+                "backward": {"ms": backward_ms, "gbs": bwd_gbs, "bytes_per_row": bwd_row},
             },
             "roofline": {
                 "kernel": "rln_backward_kernel",
@@ -523,7 +552,7 @@ def run_native_arm(args, rank, local_rank, world):
                              else "in a pass of the same steps right after the timed region"),
             },
             "cpu_baseline": cpu,
-            "e2e": None if args.kernel_only else {
+            "e2e": None if skip_e2e else {
                 "value": total_rows * e2e["steps"] / (e2e_ms * 1e-3),
                 "unit": UNIT,
                 "h2d_bytes_per_step": e2e["h2d"],

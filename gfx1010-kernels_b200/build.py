@@ -41,11 +41,18 @@ EXTENSION = PACKAGE / "_C.so"
 CUDA_SOURCES = (
     "rln_api.cu",
     "rln_forward.cu",
+    "rln_forward_narrow.cu",
     "rln_backward.cu",
+    "rln_backward_narrow.cu",
     "rln_host_pipeline.cu",
     "rln_backward_static.cu",
 )
-CUDA_HEADERS = ("rln_kernels.cuh", "rln_launch.h")
+CUDA_HEADERS = (
+    "rln_kernels.cuh",
+    "rln_launch.h",
+    "rln_forward_dispatch.cuh",
+    "rln_backward_dispatch.cuh",
+)
 NVCC_FLAGS = (
     "-gencode",
     "arch=compute_100a,code=sm_100a",

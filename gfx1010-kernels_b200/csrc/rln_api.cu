@@ -28,10 +28,11 @@ bool supported_hidden(int32_t hidden) {
         || hidden == 768 || hidden == 1024;
 }
 
-bool supported_branch(int32_t branch_dtype) {
-    return branch_dtype == RLN_BRANCH_FLOAT32 || branch_dtype == RLN_BRANCH_FLOAT16
-        || branch_dtype == RLN_BRANCH_BFLOAT16;
+bool supported_dtype(int32_t dtype) {
+    return dtype == RLN_DTYPE_FLOAT32 || dtype == RLN_DTYPE_FLOAT16 || dtype == RLN_DTYPE_BFLOAT16;
 }
+
+uintptr_t element_bytes(int32_t dtype) { return dtype == RLN_DTYPE_FLOAT32 ? 4 : 2; }
 
 bool aligned_to(const void* pointer, uintptr_t bytes) {
     return (reinterpret_cast<uintptr_t>(pointer) & (bytes - 1)) == 0;
@@ -93,6 +94,8 @@ extern "C" const char* rln_sm100_status_string(int status) {
         case RLN_ERR_HOST_BUFFERS: return "invalid host-buffer pipeline arguments";
         case RLN_ERR_LIMIT: return "size exceeds a fixed maximum of this entry point";
         case RLN_ERR_BRANCH_DTYPE: return "branch must use float32, float16 or bfloat16";
+        case RLN_ERR_NORMALIZED_DTYPE:
+            return "normalized must use float32, float16 or bfloat16";
         default: return "unknown status";
     }
 }
@@ -107,13 +110,14 @@ int forward_launch(
     const float* weight,
     const float* bias,
     float* updated,
-    float* normalized,
+    void* normalized,
     float* mean,
     float* rstd,
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
     int32_t branch_dtype,
+    int32_t normalized_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -126,8 +130,11 @@ int forward_launch(
     if (!supported_hidden(hidden)) {
         return RLN_ERR_HIDDEN_SIZE;
     }
-    if (!supported_branch(branch_dtype)) {
+    if (!supported_dtype(branch_dtype)) {
         return RLN_ERR_BRANCH_DTYPE;
+    }
+    if (!supported_dtype(normalized_dtype)) {
+        return RLN_ERR_NORMALIZED_DTYPE;
     }
     if (rows <= 0) {
         return RLN_ERR_ROW_COUNT;
@@ -143,16 +150,18 @@ int forward_launch(
         || (dropout_active && dropout_mask == nullptr)) {
         return RLN_ERR_NULL_POINTER;
     }
-    const uintptr_t branch_element = branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2;
+    const uintptr_t branch_element = element_bytes(branch_dtype);
+    const uintptr_t normalized_element = element_bytes(normalized_dtype);
     if (!aligned_to(x, 4) || !aligned_to(branch, branch_element) || !aligned_to(weight, 4)
-        || !aligned_to(bias, 4) || !aligned_to(updated, 4) || !aligned_to(normalized, 4)
+        || !aligned_to(bias, 4) || !aligned_to(updated, 4)
+        || !aligned_to(normalized, normalized_element)
         || !aligned_to(mean, 4) || !aligned_to(rstd, 4)
         || (dropout_active && !aligned_to(dropout_mask, 4))) {
         return RLN_ERR_ALIGNMENT;
     }
     const bool vector_ok = aligned_to(x, 16) && aligned_to(branch, branch_element * 4)
         && aligned_to(weight, 16) && aligned_to(bias, 16) && aligned_to(updated, 16)
-        && aligned_to(normalized, 16);
+        && aligned_to(normalized, normalized_element * 4);
 
     rln::ForwardParams params;
     params.x = x;
@@ -176,8 +185,9 @@ int forward_launch(
     params.device_seed = device_seed;
     params.device_offset = device_offset;
     params.device_offset_extra = device_seed != nullptr ? offset : 0;
-    if (device_seed != nullptr && !vector_ok) {
-        // the device-state kernels exist in the vectorised form only
+    if ((device_seed != nullptr || normalized_dtype != RLN_DTYPE_FLOAT32) && !vector_ok) {
+        // the device-state kernels and the narrow-`normalized` kernels exist in
+        // the vectorised form only
         return RLN_ERR_ALIGNMENT;
     }
 
@@ -189,6 +199,7 @@ int forward_launch(
     const cudaError_t error = rln::launch_forward(
         hidden,
         branch_dtype,
+        normalized_dtype,
         dropout_active != 0,
         vector_ok,
         params,
@@ -205,13 +216,14 @@ extern "C" int rln_sm100_forward(
     const float* weight,
     const float* bias,
     float* updated,
-    float* normalized,
+    void* normalized,
     float* mean,
     float* rstd,
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
     int32_t branch_dtype,
+    int32_t normalized_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -221,8 +233,8 @@ extern "C" int rln_sm100_forward(
     void* stream) {
     return forward_launch(
         x, branch, weight, bias, updated, normalized, mean, rstd, dropout_mask, rows, hidden,
-        branch_dtype, dropout_active, dropout_p, eps, seed, offset, nullptr, nullptr, row_base,
-        stream);
+        branch_dtype, normalized_dtype, dropout_active, dropout_p, eps, seed, offset, nullptr,
+        nullptr, row_base, stream);
 }
 
 extern "C" int rln_sm100_forward_device_rng(
@@ -231,13 +243,14 @@ extern "C" int rln_sm100_forward_device_rng(
     const float* weight,
     const float* bias,
     float* updated,
-    float* normalized,
+    void* normalized,
     float* mean,
     float* rstd,
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
     int32_t branch_dtype,
+    int32_t normalized_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -255,7 +268,7 @@ extern "C" int rln_sm100_forward_device_rng(
     }
     return forward_launch(
         x, branch, weight, bias, updated, normalized, mean, rstd, dropout_mask, rows, hidden,
-        branch_dtype, dropout_active, dropout_p, eps, 0, offset_extra,
+        branch_dtype, normalized_dtype, dropout_active, dropout_p, eps, 0, offset_extra,
         dropout_active ? device_seed : nullptr, dropout_active ? device_offset : nullptr,
         row_base, stream);
 }
@@ -284,7 +297,7 @@ extern "C" int64_t rln_sm100_backward_workspace_bytes(
 
 extern "C" int rln_sm100_backward(
     const float* grad_updated,
-    const float* grad_normalized,
+    const void* grad_normalized,
     const float* updated,
     const float* weight,
     const float* mean,
@@ -298,6 +311,7 @@ extern "C" int rln_sm100_backward(
     int64_t rows,
     int32_t hidden,
     int32_t branch_dtype,
+    int32_t normalized_dtype,
     int32_t dropout_active,
     float dropout_p,
     int32_t deterministic,
@@ -305,8 +319,11 @@ extern "C" int rln_sm100_backward(
     if (!supported_hidden(hidden)) {
         return RLN_ERR_HIDDEN_SIZE;
     }
-    if (!supported_branch(branch_dtype)) {
+    if (!supported_dtype(branch_dtype)) {
         return RLN_ERR_BRANCH_DTYPE;
+    }
+    if (!supported_dtype(normalized_dtype)) {
+        return RLN_ERR_NORMALIZED_DTYPE;
     }
     if (rows <= 0) {
         return RLN_ERR_ROW_COUNT;
@@ -319,8 +336,10 @@ extern "C" int rln_sm100_backward(
         || grad_branch == nullptr || (dropout_active && dropout_mask == nullptr)) {
         return RLN_ERR_NULL_POINTER;
     }
-    const uintptr_t branch_element = branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2;
-    if (!aligned_to(grad_updated, 4) || !aligned_to(grad_normalized, 4) || !aligned_to(updated, 4)
+    const uintptr_t branch_element = element_bytes(branch_dtype);
+    const uintptr_t normalized_element = element_bytes(normalized_dtype);
+    if (!aligned_to(grad_updated, 4) || !aligned_to(grad_normalized, normalized_element)
+        || !aligned_to(updated, 4)
         || !aligned_to(weight, 4) || !aligned_to(mean, 4) || !aligned_to(rstd, 4)
         || !aligned_to(grad_x, 4) || !aligned_to(grad_branch, branch_element)
         || (dropout_active && !aligned_to(dropout_mask, 4))
@@ -328,10 +347,15 @@ extern "C" int rln_sm100_backward(
         return RLN_ERR_ALIGNMENT;
     }
     const bool parameters = grad_parameters != nullptr;
-    const bool vector_ok = aligned_to(grad_updated, 16) && aligned_to(grad_normalized, 16)
-        && aligned_to(updated, 16) && aligned_to(weight, 16) && aligned_to(grad_x, 16)
+    const bool vector_ok = aligned_to(grad_updated, 16)
+        && aligned_to(grad_normalized, normalized_element * 4) && aligned_to(updated, 16)
+        && aligned_to(weight, 16) && aligned_to(grad_x, 16)
         && aligned_to(grad_branch, branch_element * 4)
         && (!parameters || aligned_to(grad_parameters, 16));
+    if (normalized_dtype != RLN_DTYPE_FLOAT32 && !vector_ok) {
+        // the narrow-gradient kernels exist in the vectorised form only
+        return RLN_ERR_ALIGNMENT;
+    }
 
     int sm_count = 0;
     const int status = current_sm_count(&sm_count);
@@ -378,6 +402,7 @@ extern "C" int rln_sm100_backward(
     cudaError_t error = rln::launch_backward(
         hidden,
         branch_dtype,
+        normalized_dtype,
         dropout_active != 0,
         parameters,
         vector_ok,

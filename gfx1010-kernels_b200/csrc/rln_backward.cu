@@ -1,5 +1,6 @@
-// Backward kernel instantiations, the persistent-grid rule and the dispatch ladder.
-#include "rln_launch.h"
+// Backward entry of the launch interface, the persistent-grid rule, the
+// float32-`grad_normalized` kernels and the two small helper kernels.
+#include "rln_backward_dispatch.cuh"
 
 namespace rln {
 namespace {
@@ -11,58 +12,6 @@ int backward_grid_hidden(int64_t rows, int sm_count) {
     const int64_t needed = (rows + kRowsPerCta - 1) / kRowsPerCta;
     const int64_t resident = static_cast<int64_t>(sm_count) * BackwardTune<H>::kCtasPerSm;
     return static_cast<int>(needed < resident ? needed : resident);
-}
-
-template <int H, typename BranchT, bool kDropout, bool kParams, bool kAligned>
-cudaError_t launch_backward_typed(const BackwardParams& params, int grid, cudaStream_t stream) {
-    constexpr int kWarps = BackwardTune<H>::kWarps;
-    constexpr int kRows = BackwardTune<H>::kRows;
-    return launch_dependent(
-        rln_backward_kernel<H, BranchT, kDropout, kParams, kAligned, kWarps, kRows,
-                            BackwardTune<H>::kCtasPerSm>,
-        static_cast<unsigned>(grid),
-        kWarps * kWarpSize,
-        stream,
-        params);
-}
-
-template <int H, typename BranchT, bool kAligned>
-cudaError_t launch_backward_branch(
-    bool dropout,
-    bool parameters,
-    const BackwardParams& params,
-    int grid,
-    cudaStream_t stream) {
-    if (dropout) {
-        return parameters
-            ? launch_backward_typed<H, BranchT, true, true, kAligned>(params, grid, stream)
-            : launch_backward_typed<H, BranchT, true, false, kAligned>(params, grid, stream);
-    }
-    return parameters
-        ? launch_backward_typed<H, BranchT, false, true, kAligned>(params, grid, stream)
-        : launch_backward_typed<H, BranchT, false, false, kAligned>(params, grid, stream);
-}
-
-template <int H, bool kAligned>
-cudaError_t launch_backward_hidden(
-    int branch_kind,
-    bool dropout,
-    bool parameters,
-    const BackwardParams& params,
-    int grid,
-    cudaStream_t stream) {
-    switch (branch_kind) {
-        case 0:
-            return launch_backward_branch<H, float, kAligned>(
-                dropout, parameters, params, grid, stream);
-        case 1:
-            return launch_backward_branch<H, __half, kAligned>(
-                dropout, parameters, params, grid, stream);
-        case 2:
-            return launch_backward_branch<H, __nv_bfloat16, kAligned>(
-                dropout, parameters, params, grid, stream);
-        default: return cudaErrorInvalidValue;
-    }
 }
 
 }  // namespace
@@ -82,29 +31,25 @@ int backward_grid(int hidden, int64_t rows, int sm_count) {
 cudaError_t launch_backward(
     int hidden,
     int branch_kind,
+    int normalized_kind,
     bool dropout,
     bool parameters,
     bool aligned,
     const BackwardParams& params,
     int grid,
     cudaStream_t stream) {
-#define RLN_BWD_HIDDEN(HIDDEN)                                                               \
-    case HIDDEN:                                                                             \
-        return aligned                                                                       \
-            ? launch_backward_hidden<HIDDEN, true>(                                          \
-                  branch_kind, dropout, parameters, params, grid, stream)                 \
-            : launch_backward_hidden<HIDDEN, false>(                                         \
-                  branch_kind, dropout, parameters, params, grid, stream);
-    switch (hidden) {
-        RLN_BWD_HIDDEN(128)
-        RLN_BWD_HIDDEN(256)
-        RLN_BWD_HIDDEN(384)
-        RLN_BWD_HIDDEN(512)
-        RLN_BWD_HIDDEN(768)
-        RLN_BWD_HIDDEN(1024)
+    switch (normalized_kind) {
+        case 0:
+            return launch_backward_normalized_as<float, false>(
+                hidden, branch_kind, dropout, parameters, aligned, params, grid, stream);
+        case 1:
+            return launch_backward_normalized_half(
+                hidden, branch_kind, dropout, parameters, aligned, params, grid, stream);
+        case 2:
+            return launch_backward_normalized_bfloat16(
+                hidden, branch_kind, dropout, parameters, aligned, params, grid, stream);
         default: return cudaErrorInvalidValue;
     }
-#undef RLN_BWD_HIDDEN
 }
 
 cudaError_t launch_reduce_partials(

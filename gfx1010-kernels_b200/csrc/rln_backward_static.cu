@@ -158,6 +158,7 @@ extern "C" int rln_sm100_backward_static_scratch(
     cudaError_t error = rln::launch_backward(
         hidden,
         branch_dtype,
+        RLN_DTYPE_FLOAT32,  // this entry takes a float32 grad_normalized only
         dropout_active != 0,
         /*parameters=*/true,
         vector_ok,

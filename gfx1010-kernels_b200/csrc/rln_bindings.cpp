@@ -64,6 +64,18 @@ at::ScalarType branch_dtype_from_code(int64_t code) {
     return code == RLN_BRANCH_BFLOAT16 ? at::kBFloat16 : at::kFloat;
 }
 
+// Element type of `normalized`: float32 is the reference's contract; float16
+// and bfloat16 are the narrow outputs this build adds (codes RLN_DTYPE_*).
+at::ScalarType normalized_dtype_from_code(int64_t code) {
+    TORCH_CHECK(
+        code == RLN_DTYPE_FLOAT32 || code == RLN_DTYPE_FLOAT16 || code == RLN_DTYPE_BFLOAT16,
+        "normalized_dtype must be 0 (float32), 1 (float16) or 2 (bfloat16)");
+    if (code == RLN_DTYPE_FLOAT16) {
+        return at::kHalf;
+    }
+    return code == RLN_DTYPE_BFLOAT16 ? at::kBFloat16 : at::kFloat;
+}
+
 void check_status(int status, const char* what) {
     if (status == RLN_OK) {
         return;
@@ -143,9 +155,11 @@ void check_backward_inputs(
             && weight.device() == updated.device() && mean.device() == updated.device()
             && rstd.device() == updated.device(),
         "all backward tensors must be on the same HIP device");
+    // grad_normalized has the type the forward stored `normalized` in; the
+    // reference's float32 case keeps its message.
     TORCH_CHECK(
         grad_updated.scalar_type() == at::kFloat
-            && grad_normalized.scalar_type() == at::kFloat
+            && branch_dtype_supported(grad_normalized.scalar_type())
             && updated.scalar_type() == at::kFloat && weight.scalar_type() == at::kFloat
             && mean.scalar_type() == at::kFloat && rstd.scalar_type() == at::kFloat,
         "all backward tensors must use float32");
@@ -218,14 +232,16 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> forward_l
     uint64_t offset,
     const int64_t* device_seed,
     const int64_t* device_offset,
-    int64_t row_base) {
+    int64_t row_base,
+    int64_t normalized_dtype) {
     check_forward_inputs(x, branch, weight, bias, dropout_p, eps, threads);
     TORCH_CHECK(row_base >= 0, "row_base must be non-negative");
+    const at::ScalarType normalized_type = normalized_dtype_from_code(normalized_dtype);
     c10::cuda::CUDAGuard guard(x.device());
     const int64_t hidden = x.size(-1);
     const int64_t row_count = x.numel() / hidden;
     auto updated = at::empty_like(x);
-    auto normalized = at::empty_like(x);
+    auto normalized = at::empty(x.sizes(), x.options().dtype(normalized_type));
     auto mean = at::empty({row_count}, x.options());
     auto rstd = at::empty({row_count}, x.options());
     const bool dropout = training && dropout_p > 0.0;
@@ -240,17 +256,19 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> forward_l
     if (device_seed != nullptr) {
         status = rln_sm100_forward_device_rng(
             x.data_ptr<float>(), branch.data_ptr(), weight.data_ptr<float>(),
-            bias.data_ptr<float>(), updated.data_ptr<float>(), normalized.data_ptr<float>(),
+            bias.data_ptr<float>(), updated.data_ptr<float>(), normalized.data_ptr(),
             mean.data_ptr<float>(), rstd.data_ptr<float>(), mask_pointer, row_count,
-            static_cast<int32_t>(hidden), branch_dtype, dropout ? 1 : 0,
+            static_cast<int32_t>(hidden), branch_dtype,
+            static_cast<int32_t>(normalized_dtype), dropout ? 1 : 0,
             static_cast<float>(dropout_p), static_cast<float>(eps), device_seed, device_offset,
             offset, row_base, stream);
     } else {
         status = rln_sm100_forward(
             x.data_ptr<float>(), branch.data_ptr(), weight.data_ptr<float>(),
-            bias.data_ptr<float>(), updated.data_ptr<float>(), normalized.data_ptr<float>(),
+            bias.data_ptr<float>(), updated.data_ptr<float>(), normalized.data_ptr(),
             mean.data_ptr<float>(), rstd.data_ptr<float>(), mask_pointer, row_count,
-            static_cast<int32_t>(hidden), branch_dtype, dropout ? 1 : 0,
+            static_cast<int32_t>(hidden), branch_dtype,
+            static_cast<int32_t>(normalized_dtype), dropout ? 1 : 0,
             static_cast<float>(dropout_p), static_cast<float>(eps), seed, offset, row_base,
             stream);
     }
@@ -275,10 +293,12 @@ residual_layer_norm_forward_seeded(
     int64_t threads,
     int64_t seed,
     int64_t offset,
-    int64_t row_base) {
+    int64_t row_base,
+    int64_t normalized_dtype) {
     return forward_launch(
         x, branch, weight, bias, dropout_p, eps, training, threads,
-        static_cast<uint64_t>(seed), static_cast<uint64_t>(offset), nullptr, nullptr, row_base);
+        static_cast<uint64_t>(seed), static_cast<uint64_t>(offset), nullptr, nullptr, row_base,
+        normalized_dtype);
 }
 
 // Counterpart of residual_layer_norm_forward_hip
@@ -298,8 +318,10 @@ residual_layer_norm_forward_cuda(
     double dropout_p,
     double eps,
     bool training,
-    int64_t threads) {
+    int64_t threads,
+    int64_t normalized_dtype) {
     check_forward_inputs(x, branch, weight, bias, dropout_p, eps, threads);
+    normalized_dtype_from_code(normalized_dtype);  // validate before touching the generator
     uint64_t seed = 0;
     uint64_t offset = 0;
     const int64_t* device_seed = nullptr;
@@ -336,7 +358,7 @@ residual_layer_norm_forward_cuda(
     }
     return forward_launch(
         x, branch, weight, bias, dropout_p, eps, training, threads, seed, offset, device_seed,
-        device_offset, 0);
+        device_offset, 0, normalized_dtype);
 }
 
 // Counterpart of residual_layer_norm_backward_hip
@@ -409,7 +431,7 @@ std::vector<at::Tensor> residual_layer_norm_backward_cuda(
         c10::cuda::getCurrentCUDAStream(updated.device().index()).stream();
     const int status = rln_sm100_backward(
         grad_updated.data_ptr<float>(),
-        grad_normalized.data_ptr<float>(),
+        grad_normalized.data_ptr(),
         updated.data_ptr<float>(),
         weight.data_ptr<float>(),
         mean.data_ptr<float>(),
@@ -424,6 +446,7 @@ std::vector<at::Tensor> residual_layer_norm_backward_cuda(
         row_count,
         static_cast<int32_t>(hidden),
         branch_dtype_code(branch_type),
+        branch_dtype_code(grad_normalized.scalar_type()),  // same RLN_DTYPE_* codes
         dropout ? 1 : 0,
         static_cast<float>(dropout_p),
         deterministic ? 1 : 0,
@@ -451,9 +474,10 @@ class ResidualLayerNormFunction
         int64_t threads,
         int64_t block_rows,
         int64_t parameter_threads,
-        int64_t parameter_groups) {
+        int64_t parameter_groups,
+        int64_t normalized_dtype) {
         auto result = residual_layer_norm_forward_cuda(
-            x, branch, weight, bias, dropout_p, eps, training, threads);
+            x, branch, weight, bias, dropout_p, eps, training, threads, normalized_dtype);
         auto updated = std::get<0>(result);
         auto normalized = std::get<1>(result);
         ctx->save_for_backward(
@@ -495,7 +519,7 @@ class ResidualLayerNormFunction
             ctx->saved_data["parameter_threads"].toInt(),
             ctx->saved_data["parameter_groups"].toInt(),
             has_grad_normalized);
-        torch::autograd::variable_list result(11);
+        torch::autograd::variable_list result(12);
         result[0] = gradients[0];
         result[1] = gradients[1];
         if (has_grad_normalized) {
@@ -517,7 +541,8 @@ torch::autograd::variable_list residual_layer_norm_autograd(
     int64_t threads,
     int64_t block_rows,
     int64_t parameter_threads,
-    int64_t parameter_groups) {
+    int64_t parameter_groups,
+    int64_t normalized_dtype) {
     return ResidualLayerNormFunction::apply(
         x,
         branch,
@@ -529,16 +554,36 @@ torch::autograd::variable_list residual_layer_norm_autograd(
         threads,
         block_rows,
         parameter_threads,
-        parameter_groups);
+        parameter_groups,
+        normalized_dtype);
 }
 
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, module) {
-    module.def("residual_layer_norm", &residual_layer_norm_autograd);
-    module.def("residual_layer_norm_forward", &residual_layer_norm_forward_cuda);
+    namespace py = pybind11;
+    // Positional order and arity are the reference's
+    // (csrc/residual_layer_norm_bindings.cpp:131-141); `normalized_dtype` is an
+    // optional trailing addition (0 float32 -- the reference's output type --,
+    // 1 float16, 2 bfloat16).  The backward takes the type from grad_normalized.
+    module.def(
+        "residual_layer_norm", &residual_layer_norm_autograd,
+        py::arg("x"), py::arg("branch"), py::arg("weight"), py::arg("bias"),
+        py::arg("dropout_p"), py::arg("eps"), py::arg("training"), py::arg("threads"),
+        py::arg("block_rows"), py::arg("parameter_threads"), py::arg("parameter_groups"),
+        py::arg("normalized_dtype") = 0);
+    module.def(
+        "residual_layer_norm_forward", &residual_layer_norm_forward_cuda,
+        py::arg("x"), py::arg("branch"), py::arg("weight"), py::arg("bias"),
+        py::arg("dropout_p"), py::arg("eps"), py::arg("training"), py::arg("threads"),
+        py::arg("normalized_dtype") = 0);
     module.def("residual_layer_norm_backward", &residual_layer_norm_backward_cuda);
-    module.def("residual_layer_norm_forward_seeded", &residual_layer_norm_forward_seeded);
+    module.def(
+        "residual_layer_norm_forward_seeded", &residual_layer_norm_forward_seeded,
+        py::arg("x"), py::arg("branch"), py::arg("weight"), py::arg("bias"),
+        py::arg("dropout_p"), py::arg("eps"), py::arg("training"), py::arg("threads"),
+        py::arg("seed"), py::arg("offset"), py::arg("row_base"),
+        py::arg("normalized_dtype") = 0);
     module.def("abi_version", &rln_sm100_abi_version);
     module.def("set_graph_capture_allowed", [](bool allowed) {
         graph_capture_allowed.store(allowed);

@@ -294,8 +294,8 @@ int enqueue_step(
         }
         int status = rln_sm100_forward(
             slot.x, slot.branch, p->weight, p->bias, slot.updated, slot.normalized, slot.mean,
-            slot.rstd, slot.mask, count, p->hidden, p->branch_dtype, dropout_active, dropout_p,
-            eps, seed, offset, row_base + begin, p->stream_compute);
+            slot.rstd, slot.mask, count, p->hidden, p->branch_dtype, RLN_DTYPE_FLOAT32,
+            dropout_active, dropout_p, eps, seed, offset, row_base + begin, p->stream_compute);
         if (status != RLN_OK) {
             return status;
         }
@@ -303,7 +303,7 @@ int enqueue_step(
             slot.grad_updated, slot.grad_normalized, slot.updated, p->weight, slot.mean,
             slot.rstd, slot.mask, slot.grad_x, slot.grad_branch, slot.grad_parameters,
             slot.workspace, p->workspace_bytes, count, p->hidden, p->branch_dtype,
-            dropout_active, dropout_p, deterministic, p->stream_compute);
+            RLN_DTYPE_FLOAT32, dropout_active, dropout_p, deterministic, p->stream_compute);
         if (status != RLN_OK) {
             return status;
         }

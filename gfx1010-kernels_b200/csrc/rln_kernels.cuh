@@ -41,7 +41,7 @@ struct ForwardParams {
     const float* weight;
     const float* bias;
     float* updated;
-    float* normalized;
+    void* normalized;  // float32, or float16 / bfloat16 for kernels instantiated with that NormT
     float* mean;
     float* rstd;
     uint32_t* mask;
@@ -72,7 +72,7 @@ struct PhiloxState {
 
 struct BackwardParams {
     const float* grad_updated;
-    const float* grad_normalized;
+    const void* grad_normalized;  // element type = the forward's NormT
     const float* updated;
     const float* weight;
     const float* mean;
@@ -398,7 +398,8 @@ __device__ __forceinline__ float drop_one(float b, bool keep, float scale) {
 // Forward.  grid-stride over groups of kRows consecutive rows per warp.
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kRows,
-          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = false>
+          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = false,
+          typename NormT = float>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_kernel(const ForwardParams p) {
     static_assert(H % 128 == 0, "hidden must be a multiple of 128");
@@ -523,7 +524,9 @@ rln_forward_kernel(const ForwardParams p) {
                 out.y = (u[r][k].y - row_mean) * row_rstd * gamma.y + beta.y;
                 out.z = (u[r][k].z - row_mean) * row_rstd * gamma.z + beta.z;
                 out.w = (u[r][k].w - row_mean) * row_rstd * gamma.w + beta.w;
-                store_f4<kAligned, kStreamHints>(p.normalized, row * kChunksPerRow + pchunk, out);
+                // rounded once to NormT (identity for float32)
+                BranchIO<NormT>::template store<kAligned, kStreamHints>(
+                    p.normalized, row * kChunksPerRow + pchunk, out);
             }
             if constexpr (kDropout) {
                 // chunk c = lane + 32k covers columns 4c..4c+3 -> nibble
@@ -553,7 +556,8 @@ rln_forward_kernel(const ForwardParams p) {
 // stores are predicated, shuffles are executed by the whole warp.
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kLanes,
-          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = false>
+          int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = false,
+          typename NormT = float>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_subwarp_kernel(const ForwardParams p) {
     static_assert(kLanes == 8 || kLanes == 16, "a row is owned by 8 or 16 lanes");
@@ -677,7 +681,8 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             out.z = (u[k].z - row_mean) * row_rstd * gamma.z + beta.z;
             out.w = (u[k].w - row_mean) * row_rstd * gamma.w + beta.w;
             if (valid) {
-                store_f4<kAligned, kStreamHints>(p.normalized, row * kChunksPerRow + pchunk, out);
+                BranchIO<NormT>::template store<kAligned, kStreamHints>(
+                    p.normalized, row * kChunksPerRow + pchunk, out);
             }
         }
         if constexpr (kDropout) {
@@ -709,7 +714,7 @@ __device__ __forceinline__ void red_add_f4(float* address, float4 v) {
 }
 
 template <int H, typename BranchT, bool kDropout, bool kParams, bool kAligned, int kWarps, int kRows,
-          int kMinCtas = 1, bool kStreamHints = false>
+          int kMinCtas = 1, bool kStreamHints = false, typename NormT = float>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_backward_kernel(const BackwardParams p) {
     static_assert(H % 128 == 0, "hidden must be a multiple of 128");
@@ -753,7 +758,8 @@ rln_backward_kernel(const BackwardParams p) {
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
                     const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
-                    gy[r][k] = load_f4<kAligned, kStreamHints>(p.grad_normalized, chunk);
+                    gy[r][k] = BranchIO<NormT>::template load<kAligned, kStreamHints>(
+                        p.grad_normalized, chunk);
                     uu[r][k] = load_f4<kAligned, kStreamHints>(p.updated, chunk);
                     gu[r][k] = load_f4<kAligned, kStreamHints>(p.grad_updated, chunk);
                     if constexpr (kDropout) {

@@ -93,10 +93,14 @@ int record_cuda_error(cudaError_t error);
 // arguments; also the number of [2, hidden] partials in deterministic mode).
 int backward_grid(int hidden, int64_t rows, int sm_count);
 
-// branch_kind: RLN_BRANCH_FLOAT32 / FLOAT16 / BFLOAT16 (0 / 1 / 2).
+// branch_kind / normalized_kind: RLN_DTYPE_FLOAT32 / FLOAT16 / BFLOAT16
+// (0 / 1 / 2).  normalized_kind is the element type of `normalized` (forward)
+// and of `grad_normalized` (backward); kinds 1 and 2 exist for 16-byte aligned
+// pointers only and return cudaErrorNotSupported otherwise.
 cudaError_t launch_forward(
     int hidden,
     int branch_kind,
+    int normalized_kind,
     bool dropout,
     bool aligned,
     const ForwardParams& params,
@@ -106,12 +110,28 @@ cudaError_t launch_forward(
 cudaError_t launch_backward(
     int hidden,
     int branch_kind,
+    int normalized_kind,
     bool dropout,
     bool parameters,
     bool aligned,
     const BackwardParams& params,
     int grid,
     cudaStream_t stream);
+
+// The narrow-`normalized` halves of the two ladders live in translation units
+// of their own (rln_forward_narrow.cu, rln_backward_narrow.cu).
+cudaError_t launch_forward_normalized_half(
+    int hidden, int branch_kind, bool dropout, bool aligned,
+    const ForwardParams& params, int sm_count, cudaStream_t stream);
+cudaError_t launch_forward_normalized_bfloat16(
+    int hidden, int branch_kind, bool dropout, bool aligned,
+    const ForwardParams& params, int sm_count, cudaStream_t stream);
+cudaError_t launch_backward_normalized_half(
+    int hidden, int branch_kind, bool dropout, bool parameters, bool aligned,
+    const BackwardParams& params, int grid, cudaStream_t stream);
+cudaError_t launch_backward_normalized_bfloat16(
+    int hidden, int branch_kind, bool dropout, bool parameters, bool aligned,
+    const BackwardParams& params, int grid, cudaStream_t stream);
 
 // Zeroes `count` floats (count % 4 == 0, 16-byte aligned) with a kernel instead
 // of a memset node, which keeps the step's launches kernel -> kernel.

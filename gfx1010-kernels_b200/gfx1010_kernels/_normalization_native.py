@@ -17,6 +17,8 @@ later random ops identical to the reference's.
 from bisect import bisect_left
 from functools import lru_cache
 
+import torch
+
 
 NATIVE_HIDDEN_SIZES = (128, 256, 384, 512, 768, 1024)
 
@@ -76,7 +78,22 @@ def native_extension_status():
     return extension is not None, reason
 
 
-def native_residual_layer_norm(x, branch, weight, bias, dropout_p, eps, training):
+# extension codes of the ``normalized`` element type (RLN_DTYPE_* of the C header)
+NORMALIZED_DTYPE_CODES = {None: 0, torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def normalized_dtype_code(normalized_dtype):
+    """Extension code of ``normalized_dtype`` (None = float32); ValueError otherwise."""
+    try:
+        return NORMALIZED_DTYPE_CODES[normalized_dtype]
+    except (KeyError, TypeError):
+        raise ValueError(
+            "normalized_dtype must be None, torch.float32, torch.float16 or torch.bfloat16"
+        ) from None
+
+
+def native_residual_layer_norm(x, branch, weight, bias, dropout_p, eps, training,
+                               normalized_dtype=None):
     """Call the autograd-connected extension entry; no Python-side validation.
 
     There is deliberately no fallback here: a missing extension raises.
@@ -98,5 +115,6 @@ def native_residual_layer_norm(x, branch, weight, bias, dropout_p, eps, training
         _block_rows(hidden_size, row_count),
         _parameter_threads(hidden_size, row_count),
         _parameter_groups(hidden_size, row_count),
+        normalized_dtype_code(normalized_dtype),
     )
     return tuple(outputs)

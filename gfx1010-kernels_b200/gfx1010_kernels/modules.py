@@ -31,7 +31,7 @@ class ResidualLayerNorm(nn.LayerNorm):
     """
 
     def __init__(self, hidden_size, dropout_p=0.0, eps=1e-5, implementation="auto",
-                 device=None, dtype=torch.float32):
+                 device=None, dtype=torch.float32, normalized_dtype=None):
         if isinstance(hidden_size, (tuple, list, torch.Size)):
             if len(hidden_size) != 1:
                 raise ValueError("ResidualLayerNorm normalises over the last dimension only")
@@ -42,6 +42,9 @@ class ResidualLayerNorm(nn.LayerNorm):
             raise ValueError("dropout_p must be in [0, 1)")
         self.dropout_p = float(dropout_p)
         self.implementation = implementation
+        # None = float32; torch.bfloat16 / torch.float16 hand the following GEMM
+        # a half-precision activation without a separate cast kernel
+        self.normalized_dtype = normalized_dtype
 
     @property
     def native_width(self):
@@ -50,9 +53,12 @@ class ResidualLayerNorm(nn.LayerNorm):
     def forward(self, x, branch):  # noqa: D102 - see the class docstring
         return residual_layer_norm(
             x, branch, self.weight, self.bias, self.dropout_p, self.eps, self.training,
-            implementation=self.implementation,
+            implementation=self.implementation, normalized_dtype=self.normalized_dtype,
         )
 
     def extra_repr(self):
-        return (f"{self.normalized_shape[0]}, eps={self.eps}, dropout_p={self.dropout_p}, "
+        text = (f"{self.normalized_shape[0]}, eps={self.eps}, dropout_p={self.dropout_p}, "
                 f"implementation={self.implementation!r}")
+        if self.normalized_dtype is not None:
+            text += f", normalized_dtype={self.normalized_dtype}"
+        return text

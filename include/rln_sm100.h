@@ -44,7 +44,8 @@ extern "C" {
 #define RLN_ERR_CUDA (-8)               /* a CUDA runtime call failed; see rln_sm100_last_cuda_error */
 #define RLN_ERR_HOST_BUFFERS (-9)       /* host-buffer pipeline: bad chunk size or context */
 #define RLN_ERR_LIMIT (-10)             /* size beyond a documented fixed maximum */
-#define RLN_ERR_BRANCH_DTYPE (-11)      /* branch_dtype is not one of RLN_BRANCH_* */
+#define RLN_ERR_BRANCH_DTYPE (-11)      /* branch_dtype is not one of RLN_DTYPE_* */
+#define RLN_ERR_NORMALIZED_DTYPE (-12)  /* normalized_dtype is not one of RLN_DTYPE_* */
 
 /* Element type of `branch` / `grad_branch`.  0 and 1 are the reference's two
  * cases (its entry points carry a bool "branch is half",
@@ -52,12 +53,26 @@ extern "C" {
  * training on this hardware.  Rounding rule for all three: the dropped branch
  * is float32(b) * keep * scale rounded once to the branch type, grad_branch is
  * the float32 gradient * keep * scale rounded once to the branch type. */
-#define RLN_BRANCH_FLOAT32 0
-#define RLN_BRANCH_FLOAT16 1
-#define RLN_BRANCH_BFLOAT16 2
+#define RLN_DTYPE_FLOAT32 0
+#define RLN_DTYPE_FLOAT16 1
+#define RLN_DTYPE_BFLOAT16 2
+#define RLN_BRANCH_FLOAT32 RLN_DTYPE_FLOAT32
+#define RLN_BRANCH_FLOAT16 RLN_DTYPE_FLOAT16
+#define RLN_BRANCH_BFLOAT16 RLN_DTYPE_BFLOAT16
+
+/* Element type of `normalized` (forward) and of `grad_normalized` (backward),
+ * the same RLN_DTYPE_* codes.  RLN_DTYPE_FLOAT32 is the reference's contract
+ * (csrc/residual_layer_norm_kernel.hip:1746-1747: both outputs float32).  The
+ * two 16-bit types are an addition for a consumer that feeds `normalized` to a
+ * half-precision GEMM: the float32 result is rounded once (to nearest even) on
+ * store, the incoming gradient is widened on load, everything in between is
+ * the same float32 arithmetic, and the operator moves 2 bytes less per element
+ * in each direction.  They need the 16-byte pointer alignment of the
+ * vectorised kernels (8-byte for the 16-bit tensors): RLN_ERR_ALIGNMENT
+ * otherwise. */
 
 /* ABI version of this header; bumped on any signature change. */
-#define RLN_SM100_ABI_VERSION 3
+#define RLN_SM100_ABI_VERSION 4
 RLN_API int rln_sm100_abi_version(void);
 
 /* Human-readable text for a status code (static storage, never NULL). */
@@ -75,10 +90,10 @@ RLN_API int rln_sm100_last_cuda_error(void);
  * and the kernels it dispatches (forward kernel :425-545, vector4 kernel :353-422).
  *
  *   x            device, float32 [rows, hidden]
- *   branch       device, float32 / float16 / bfloat16 per branch_dtype (RLN_BRANCH_*), [rows, hidden]
+ *   branch       device, float32 / float16 / bfloat16 per branch_dtype (RLN_DTYPE_*), [rows, hidden]
  *   weight, bias device, float32 [hidden]
  *   updated      device out, float32 [rows, hidden]
- *   normalized   device out, float32 [rows, hidden]
+ *   normalized   device out, float32 / float16 / bfloat16 per normalized_dtype, [rows, hidden]
  *   mean, rstd   device out, float32 [rows]   (rstd = rsqrt(centred variance + eps))
  *   dropout_mask device out, uint32 [rows * hidden/32]; bit (col & 31) of word
  *                row*(hidden/32) + col/32 is 1 when the element was kept
@@ -104,13 +119,14 @@ RLN_API int rln_sm100_forward(
     const float* weight,
     const float* bias,
     float* updated,
-    float* normalized,
+    void* normalized,
     float* mean,
     float* rstd,
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
     int32_t branch_dtype,
+    int32_t normalized_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -139,13 +155,14 @@ RLN_API int rln_sm100_forward_device_rng(
     const float* weight,
     const float* bias,
     float* updated,
-    float* normalized,
+    void* normalized,
     float* mean,
     float* rstd,
     uint32_t* dropout_mask,
     int64_t rows,
     int32_t hidden,
     int32_t branch_dtype,
+    int32_t normalized_dtype,
     int32_t dropout_active,
     float dropout_p,
     float eps,
@@ -178,7 +195,10 @@ RLN_API int64_t rln_sm100_backward_workspace_bytes(
  * and its kernels: backward-input :548-618 / :621-724, deterministic partials +
  * reduce :727-786, atomic parameter kernels :789-869.
  *
- *   grad_updated, grad_normalized, updated   device, float32 [rows, hidden]
+ *   grad_updated, updated                    device, float32 [rows, hidden]
+ *   grad_normalized                          device, [rows, hidden] in the type
+ *                                            the forward stored `normalized` in
+ *                                            (normalized_dtype, RLN_DTYPE_*)
  *   weight                                   device, float32 [hidden]
  *   mean, rstd                               device, float32 [rows]
  *   dropout_mask     device, uint32 [rows*hidden/32] (ignored when dropout_active == 0)
@@ -200,7 +220,7 @@ RLN_API int64_t rln_sm100_backward_workspace_bytes(
  */
 RLN_API int rln_sm100_backward(
     const float* grad_updated,
-    const float* grad_normalized,
+    const void* grad_normalized,
     const float* updated,
     const float* weight,
     const float* mean,
@@ -214,6 +234,7 @@ RLN_API int rln_sm100_backward(
     int64_t rows,
     int32_t hidden,
     int32_t branch_dtype,
+    int32_t normalized_dtype,
     int32_t dropout_active,
     float dropout_p,
     int32_t deterministic,
@@ -221,7 +242,8 @@ RLN_API int rln_sm100_backward(
 
 /*
  * Backward for callers that must not allocate: same outputs as
- * rln_sm100_backward(..., deterministic = 1) with parameter gradients, but the
+ * rln_sm100_backward(..., normalized_dtype = RLN_DTYPE_FLOAT32,
+ * deterministic = 1) with parameter gradients, but the
  * per-CTA partials are kept in a scratch array built into this library's
  * device image, so no workspace is passed and nothing is allocated -- not by
  * this call and not by anything it calls.

@@ -45,8 +45,12 @@ def keep_mask(rows, hidden, dropout_p, seed, offset, row_base=0):
     return keep.astype(bool), words.view(np.int32)
 
 
-def forward(x, branch, weight, bias, keep, dropout_p, eps, branch_kind):
-    """``branch_kind``: 0/False float32, 1/True float16, 2 bfloat16."""
+def forward(x, branch, weight, bias, keep, dropout_p, eps, branch_kind, normalized_kind=0):
+    """``branch_kind`` / ``normalized_kind``: 0/False float32, 1/True float16, 2 bfloat16.
+
+    ``normalized`` is returned as float32 values that are exactly representable
+    in the ``normalized_kind`` type (rounded once from the float32 result).
+    """
     x = np.ascontiguousarray(x, dtype=np.float32)
     rows, hidden = x.shape
     branch = np.ascontiguousarray(branch, dtype=np.float32)
@@ -64,6 +68,10 @@ def forward(x, branch, weight, bias, keep, dropout_p, eps, branch_kind):
         ctypes.c_int64(rows), ctypes.c_int32(hidden),
         _p(updated), _p(normalized), _p(mean), _p(rstd),
     )
+    if int(normalized_kind) != 0:
+        _lib().rln_oracle_round(
+            _p(normalized), ctypes.c_int64(normalized.size), ctypes.c_int32(int(normalized_kind))
+        )
     return updated, normalized, mean, rstd
 
 

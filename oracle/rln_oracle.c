@@ -69,6 +69,13 @@ static float round_branch(float v, int32_t branch_kind) {
     return v;
 }
 
+/* In place: values[i] = widen(round_to_kind(values[i])).  Used for a
+ * `normalized` output stored as float16 / bfloat16 (an addition of the sm_100a
+ * build; the reference stores float32): rounded once, to nearest even. */
+void rln_oracle_round(float* values, int64_t count, int32_t kind) {
+    for (int64_t i = 0; i < count; ++i) values[i] = round_branch(values[i], kind);
+}
+
 /* keep[rows * hidden] (0/1 bytes) and mask words [rows * hidden / 32]. */
 void rln_oracle_keep_mask(
     int64_t rows, int32_t hidden, float dropout_p, uint64_t seed, uint64_t offset,

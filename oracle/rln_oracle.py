@@ -165,12 +165,15 @@ def torch_decomposition(
     eps=1e-5,
     training=True,
     keep=None,
+    normalized_dtype=None,
 ):
     """``normalization.py:15-33`` with the dropout mask supplied by the caller.
 
     ``keep=None`` with active dropout falls back to ``F.dropout`` exactly as the
     reference does (used only for timing the CPU baseline, where the mask values
-    do not matter).
+    do not matter).  ``normalized_dtype`` (float16 / bfloat16; not part of the
+    reference) rounds ``normalized`` once at the end, as the native kernels do
+    on store; autograd then widens the incoming gradient.
     """
     active = training and dropout_p > 0.0
     if active and keep is not None:
@@ -181,6 +184,8 @@ def torch_decomposition(
         dropped = branch
     updated = x + dropped
     normalized = F.layer_norm(updated, (updated.shape[-1],), weight, bias, eps)
+    if normalized_dtype is not None and normalized_dtype != normalized.dtype:
+        normalized = normalized.to(normalized_dtype)
     return updated, normalized
 
 
@@ -205,19 +210,22 @@ def decomposition_gradients(
     training=True,
     keep=None,
     dtype=None,
+    normalized_dtype=None,
 ):
     """Forward + autograd through ``torch_decomposition``.
 
     ``dtype=torch.float64`` gives the arbiter copy: all tensors are widened
     AFTER the branch-dtype rounding of the dropped branch, so the arbiter sees
-    the same ``updated`` values as the fp32 path.
+    the same ``updated`` values as the fp32 path.  With ``normalized_dtype``
+    the fp32 path returns ``normalized`` in that type and expects
+    ``grad_normalized`` in it; the arbiter keeps ``normalized`` unrounded.
     Returns ``(updated, normalized, grad_x, grad_branch, grad_weight, grad_bias)``.
     """
     leaves = [t.detach().clone().requires_grad_(True) for t in (x, branch, weight, bias)]
     lx, lb, lw, lbias = leaves
     if dtype is None:
         updated, normalized = torch_decomposition(
-            lx, lb, lw, lbias, dropout_p, eps, training, keep
+            lx, lb, lw, lbias, dropout_p, eps, training, keep, normalized_dtype
         )
     else:
         active = training and dropout_p > 0.0

@@ -21,7 +21,9 @@ _u64 = ctypes.c_uint64
 _f32 = ctypes.c_float
 
 _library = None
-BRANCH_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+# RLN_DTYPE_* of include/rln_sm100.h (branch and normalized element types)
+DTYPE_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+BRANCH_CODES = DTYPE_CODES
 
 
 def library():
@@ -35,14 +37,14 @@ def library():
         lib.rln_sm100_forward.restype = ctypes.c_int
         lib.rln_sm100_forward.argtypes = [
             _p, _p, _p, _p, _p, _p, _p, _p, _p,
-            _i64, _i32, _i32, _i32, _f32, _f32, _u64, _u64, _i64, _p,
+            _i64, _i32, _i32, _i32, _i32, _f32, _f32, _u64, _u64, _i64, _p,
         ]
         lib.rln_sm100_backward_workspace_bytes.restype = _i64
         lib.rln_sm100_backward_workspace_bytes.argtypes = [_i64, _i32, _i32]
         lib.rln_sm100_backward.restype = ctypes.c_int
         lib.rln_sm100_backward.argtypes = [
             _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p,
-            _i64, _i64, _i32, _i32, _i32, _f32, _i32, _p,
+            _i64, _i64, _i32, _i32, _i32, _i32, _f32, _i32, _p,
         ]
         _library = lib
     return _library
@@ -61,14 +63,14 @@ def status_text(status):
 
 
 def forward(x, branch, weight, bias, dropout_p, eps, training, seed=0, offset=0, row_base=0,
-            outputs=None):
+            outputs=None, normalized_dtype=torch.float32):
     """Returns (status, updated, normalized, mean, rstd, mask)."""
     hidden = x.shape[-1]
     rows = x.numel() // hidden
     active = bool(training and dropout_p > 0.0)
     if outputs is None:
         updated = torch.empty_like(x)
-        normalized = torch.empty_like(x)
+        normalized = torch.empty(x.shape, dtype=normalized_dtype, device=x.device)
         mean = torch.empty(rows, device=x.device)
         rstd = torch.empty(rows, device=x.device)
         mask = torch.empty(
@@ -80,7 +82,7 @@ def forward(x, branch, weight, bias, dropout_p, eps, training, seed=0, offset=0,
         _ptr(x), _ptr(branch), _ptr(weight), _ptr(bias),
         _ptr(updated), _ptr(normalized), _ptr(mean), _ptr(rstd),
         _ptr(mask) if active else None,
-        rows, hidden, BRANCH_CODES[branch.dtype], int(active),
+        rows, hidden, DTYPE_CODES[branch.dtype], DTYPE_CODES[normalized.dtype], int(active),
         dropout_p, eps, seed, offset, row_base, _stream(),
     )
     return status, updated, normalized, mean, rstd, mask
@@ -110,7 +112,8 @@ def backward(grad_updated, grad_normalized, updated, weight, mean, rstd, mask, d
         _ptr(grad_updated), _ptr(grad_normalized), _ptr(updated), _ptr(weight),
         _ptr(mean), _ptr(rstd), _ptr(mask) if active else None,
         _ptr(grad_x), _ptr(grad_branch), _ptr(grad_parameters), _ptr(workspace),
-        workspace_bytes, rows, hidden, BRANCH_CODES[branch_dtype], int(active),
+        workspace_bytes, rows, hidden, DTYPE_CODES[branch_dtype],
+        DTYPE_CODES[grad_normalized.dtype], int(active),
         dropout_p, int(deterministic), _stream(),
     )
     return status, grad_x, grad_branch, grad_parameters

@@ -65,11 +65,13 @@ def golden_cases():
 
 def golden_tensors(case, device="cpu"):
     """The arrays of one golden case as torch tensors, with ``branch`` and
-    ``grad_branch`` in the case's branch dtype (bfloat16 is stored widened to
-    float32, which represents it exactly)."""
+    ``grad_branch`` in the case's branch dtype and ``normalized`` /
+    ``grad_normalized`` in its normalized dtype (16-bit values are stored
+    widened to float32, which represents them exactly)."""
     import torch
 
     dtype = getattr(torch, case["meta"]["branch_dtype"])
+    normalized_dtype = getattr(torch, case["meta"].get("normalized_dtype", "float32"))
     tensors = {}
     for key, value in case.items():
         if key in ("meta", "config"):
@@ -77,6 +79,8 @@ def golden_tensors(case, device="cpu"):
         tensor = torch.from_numpy(value)
         if key in ("branch", "grad_branch"):
             tensor = tensor.to(dtype)
+        elif key in ("normalized", "grad_normalized"):
+            tensor = tensor.to(normalized_dtype)
         tensors[key] = tensor.to(device)
     return tensors
 

@@ -49,7 +49,21 @@ CASES = (
     # bfloat16 branch (an addition of the sm_100a build; the reference's own
     # decomposition handles it through torch's type promotion)
     ("h768_bfloat16_p10", (4,), 768, "bfloat16", 0.10, 1e-5, True, 6, 99, 12),
+    # `normalized` stored in a 16-bit type (another addition; trailing field).
+    # The reference function runs unchanged; this script casts its float32
+    # `normalized` once and sends the 16-bit upstream gradient back through
+    # that cast, which is what the native kernels do on store / load.
+    ("h768_half_p10_bf16norm", (6,), 768, "float16", 0.10, 1e-5, True, 7, 5, 16, "bfloat16"),
+    ("h256_bfloat16_p20_f16norm", (3,), 256, "bfloat16", 0.20, 1e-5, True, 8, 11, 0, "float16"),
+    ("h1024_float_eval_bf16norm", (5,), 1024, "float32", 0.30, 1e-5, False, 9, 0, 0, "bfloat16"),
 )
+
+
+def unpack_case(case):
+    """The ten base fields plus the optional ``normalized`` dtype name."""
+    base = case[:10]
+    normalized_dtype = case[10] if len(case) > 10 else "float32"
+    return (*base, normalized_dtype)
 
 PHILOX_KAT = (
     # Random123 kat_vectors, philox4x32 with 10 rounds
@@ -84,7 +98,9 @@ def main():
 
     arrays = {}
     names = []
-    for (name, shape, hidden, branch_dtype, p, eps, training, seed, pseed, poffset) in CASES:
+    for case in CASES:
+        (name, shape, hidden, branch_dtype, p, eps, training, seed, pseed, poffset,
+         normalized_dtype) = unpack_case(case)
         x, branch, weight, bias, grad_updated, grad_normalized = draw_inputs(
             shape, hidden, branch_dtype, seed
         )
@@ -107,6 +123,9 @@ def main():
             updated, normalized = reference._torch_residual_layer_norm(
                 *leaves, p, eps, training
             )
+            if normalized_dtype != "float32":
+                normalized = normalized.to(getattr(torch, normalized_dtype))
+                grad_normalized = grad_normalized.to(normalized.dtype)
             grads = torch.autograd.grad(
                 (updated, normalized), leaves, (grad_updated, grad_normalized)
             )
@@ -122,8 +141,9 @@ def main():
             "grad_weight": grads[2], "grad_bias": grads[3],
         }
         for key, tensor in record.items():
-            if tensor.dtype == torch.bfloat16:
-                tensor = tensor.float()  # numpy has no bfloat16; the values are exact in fp32
+            if tensor.dtype == torch.bfloat16 or (
+                    key in ("normalized", "grad_normalized") and tensor.dtype == torch.float16):
+                tensor = tensor.float()  # exact in fp32; numpy has no bfloat16
             arrays[f"{name}/{key}"] = tensor.numpy()
         arrays[f"{name}/mask"] = (
             rln_oracle.pack_mask(keep) if active else np.zeros(0, dtype=np.int32)
@@ -141,9 +161,10 @@ def main():
                 "branch_dtype": branch_dtype, "dropout_p": p, "eps": eps,
                 "training": training, "input_seed": seed,
                 "philox_seed": pseed, "philox_offset": poffset,
+                "normalized_dtype": normalized_dtype,
             }
-            for (name, shape, hidden, branch_dtype, p, eps, training, seed, pseed, poffset)
-            in CASES
+            for (name, shape, hidden, branch_dtype, p, eps, training, seed, pseed, poffset,
+                 normalized_dtype) in map(unpack_case, CASES)
         ],
         "torch_version": torch.__version__,
         "reference": "T-vaccari/gfx1010-kernels 0.4.0, "

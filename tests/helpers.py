@@ -23,6 +23,28 @@ def grad_branch_tolerance(branch_dtype):
     if branch_dtype == _torch.bfloat16:
         return GRAD_BRANCH_BF16_TOL
     return GRAD_X_TOL
+
+
+def assert_narrow_normalized(actual, reference64, what="normalized"):
+    """``actual`` (float16 / bfloat16) is the single rounding of a float32 value
+    within NORMALIZED_TOL of ``reference64``.
+
+    Rounding to nearest is monotonic, so a float32 result in
+    ``[r - tol, r + tol]`` must round into ``[round(r - tol), round(r + tol)]``:
+    the check is exact, with no extra slack for the 16-bit type.
+    """
+    reference64 = reference64.double().reshape(actual.shape)
+    tolerance = NORMALIZED_TOL["atol"] + NORMALIZED_TOL["rtol"] * reference64.abs()
+    low = (reference64 - tolerance).float().to(actual.dtype).double()
+    high = (reference64 + tolerance).float().to(actual.dtype).double()
+    value = actual.double()
+    inside = (value >= low) & (value <= high)
+    assert bool(inside.all()), (
+        f"{what}: {int((~inside).sum())} of {inside.numel()} elements are not the rounding "
+        f"of a float32-close value"
+    )
+
+
 PARAM_RTOL = 1e-4                                 # grad_weight / grad_bias, relative
 
 

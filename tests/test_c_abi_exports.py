@@ -60,10 +60,11 @@ def test_argument_validation_precedes_any_cuda_call(built_libraries):
     null = ctypes.c_void_p(None)
     fake = ctypes.c_void_p(0x1000)
 
-    def forward(rows=4, hidden=128, p=0.1, eps=1e-5, x=fake):
+    def forward(rows=4, hidden=128, p=0.1, eps=1e-5, x=fake, branch_dtype=1, normalized_dtype=0,
+                normalized=fake):
         return lib.rln_sm100_forward(
-            x, fake, fake, fake, fake, fake, fake, fake, fake,
-            rows, hidden, 1, 1, p, eps, 0, 0, 0, null,
+            x, fake, fake, fake, fake, normalized, fake, fake, fake,
+            rows, hidden, branch_dtype, normalized_dtype, 1, p, eps, 0, 0, 0, null,
         )
 
     assert forward(hidden=160) == -2
@@ -73,6 +74,12 @@ def test_argument_validation_precedes_any_cuda_call(built_libraries):
     assert forward(eps=0.0) == -5
     assert forward(x=null) == -1
     assert forward(x=ctypes.c_void_p(0x1002)) == -6
+    assert forward(branch_dtype=3) == -11
+    assert forward(normalized_dtype=3) == -12
+    assert forward(normalized_dtype=-1) == -12
+    # a 16-bit `normalized` has no scalar-access kernel: 8-byte alignment or nothing
+    assert forward(normalized_dtype=2, normalized=ctypes.c_void_p(0x1004)) == -6
+    assert forward(normalized_dtype=0, normalized=ctypes.c_void_p(0x1002)) == -6
     assert lib.rln_sm100_backward_workspace_bytes(0, 128, 1) == -3
     assert lib.rln_sm100_backward_workspace_bytes(16, 100, 1) == -2
     assert lib.rln_sm100_backward_workspace_bytes(16, 128, 0) == 0

@@ -260,3 +260,56 @@ def test_extension_keeps_the_reference_entry_points(built_libraries):
         "residual_layer_norm_backward",
     ):
         assert callable(getattr(_C, name))
+
+
+@pytest.mark.parametrize("normalized_dtype", [torch.float16, torch.bfloat16])
+def test_torch_route_casts_normalized_once_and_stays_differentiable(normalized_dtype):
+    torch.manual_seed(7)
+    tensors = [torch.randn(5, 256), torch.randn(5, 256), torch.randn(256), torch.randn(256)]
+    plain = residual_layer_norm(*tensors, implementation="torch")
+    leaves = [t.clone().requires_grad_(True) for t in tensors]
+    updated, normalized = residual_layer_norm(
+        *leaves, implementation="torch", normalized_dtype=normalized_dtype
+    )
+    assert updated.dtype == torch.float32 and normalized.dtype == normalized_dtype
+    assert torch.equal(updated, plain[0])
+    assert torch.equal(normalized, plain[1].to(normalized_dtype))
+    grads = torch.autograd.grad(
+        (updated, normalized), leaves,
+        (torch.ones_like(updated), torch.ones_like(normalized)),
+    )
+    assert [g.dtype for g in grads] == [torch.float32] * 4
+    # float32 is the default spelled out
+    same = residual_layer_norm(*tensors, implementation="torch", normalized_dtype=torch.float32)
+    assert same[1].dtype == torch.float32 and torch.equal(same[1], plain[1])
+
+
+def test_auto_fallback_honours_normalized_dtype():
+    tensors = [torch.randn(2, 128), torch.randn(2, 128), torch.ones(128), torch.zeros(128)]
+    with pytest.warns(RuntimeWarning, match="was not used"):
+        _, normalized = residual_layer_norm(*tensors, normalized_dtype=torch.bfloat16)
+    assert normalized.dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("bad", [torch.float64, torch.int32, "bfloat16"])
+def test_unsupported_normalized_dtype_is_a_value_error(bad):
+    tensors = [torch.randn(2, 128), torch.randn(2, 128), torch.ones(128), torch.zeros(128)]
+    for implementation in ("torch", "auto", "gfx1010"):
+        with pytest.raises(ValueError, match="normalized_dtype"):
+            residual_layer_norm(*tensors, implementation=implementation, normalized_dtype=bad)
+
+
+def test_extension_signatures_keep_the_reference_arity_with_an_optional_tail(built_libraries):
+    """The reference's positional calls still bind; `normalized_dtype` is a
+    trailing optional argument of the three forward-side entries."""
+    from gfx1010_kernels import _C
+
+    doc = _C.residual_layer_norm.__doc__
+    assert "parameter_groups: typing.SupportsInt" in doc or "parameter_groups: int" in doc
+    assert "normalized_dtype" in doc and "= 0" in doc
+    assert "normalized_dtype" in _C.residual_layer_norm_forward.__doc__
+    assert "normalized_dtype" in _C.residual_layer_norm_forward_seeded.__doc__
+    assert "normalized_dtype" not in _C.residual_layer_norm_backward.__doc__
+    x = torch.randn(2, 128)
+    with pytest.raises(RuntimeError, match="x must be a HIP tensor"):
+        _C.residual_layer_norm_forward(x, x, x[0], x[0], 0.0, 1e-5, True, 128, 2)

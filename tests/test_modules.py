@@ -67,3 +67,11 @@ def test_module_runs_the_native_kernels_on_gpu():
     )
     (updated.square().sum() + normalized.sum()).backward()
     assert module.weight.grad.shape == (768,) and x.grad is not None and branch.grad is not None
+
+
+def test_module_passes_normalized_dtype_through():
+    module = ResidualLayerNorm(128, implementation="torch", normalized_dtype=torch.bfloat16)
+    updated, normalized = module(torch.randn(3, 128), torch.randn(3, 128))
+    assert updated.dtype == torch.float32 and normalized.dtype == torch.bfloat16
+    assert "normalized_dtype=torch.bfloat16" in repr(module)
+    assert "normalized_dtype" not in repr(ResidualLayerNorm(128))

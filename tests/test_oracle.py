@@ -77,6 +77,9 @@ def test_kept_fraction_is_within_four_sigma():
         "h768_half_p10",
         "h1024_float_p25",
         "h768_bfloat16_p10",
+        "h768_half_p10_bf16norm",
+        "h256_bfloat16_p20_f16norm",
+        "h1024_float_eval_bf16norm",
     ],
 )
 def test_oracle_reproduces_reference_fixtures(golden_cases, name):
@@ -97,6 +100,7 @@ def test_oracle_reproduces_reference_fixtures(golden_cases, name):
         tensors["x"], tensors["branch"], tensors["weight"], tensors["bias"],
         tensors["grad_updated"], tensors["grad_normalized"],
         meta["dropout_p"], meta["eps"], meta["training"], keep,
+        normalized_dtype=tensors["normalized"].dtype,
     )
     names = ("updated", "normalized", "grad_x", "grad_branch", "grad_weight", "grad_bias")
     for key, actual in zip(names, result):

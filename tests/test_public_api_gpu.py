@@ -564,3 +564,74 @@ def test_bfloat16_branch_forward_and_backward():
                                   implementation="gfx1010")[0]
     kept_value = torch.tensor(1.0 / (1.0 - 0.3), dtype=torch.float32).to(torch.bfloat16).float()
     assert set(updated.unique().tolist()) <= {0.0, kept_value.item()}
+
+
+@pytest.mark.parametrize("normalized_dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("hidden", [128, 768, 1024])
+def test_narrow_normalized_output_through_autograd(hidden, normalized_dtype):
+    """`normalized_dtype=`: the native route returns `normalized` in a 16-bit
+    type and takes its gradient in that type; compared with the decomposition
+    followed by one cast (torch autograd widens the gradient through the cast)."""
+    torch.manual_seed(263 + hidden)
+    data = random_inputs(41, hidden, leading=(2,))
+    actual_inputs = leaves(data)
+    expected_inputs = leaves(data)
+    actual = residual_layer_norm(
+        *actual_inputs, implementation="gfx1010", normalized_dtype=normalized_dtype
+    )
+    expected = decomposition(*expected_inputs)
+    expected = (expected[0], expected[1].to(normalized_dtype))
+    assert actual[0].dtype == torch.float32 and actual[1].dtype == normalized_dtype
+    torch.testing.assert_close(actual[0], expected[0], rtol=0, atol=0)
+    # one rounding of float32 values that agree to 1e-5: neighbours at worst
+    tolerance = {torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[normalized_dtype]
+    torch.testing.assert_close(actual[1].float(), expected[1].float(), rtol=tolerance, atol=1e-4)
+    assert (actual[1] == expected[1]).float().mean().item() > 0.99
+    grad_updated = torch.randn_like(actual[0])
+    grad_normalized = torch.randn_like(actual[1])
+    assert grad_normalized.dtype == normalized_dtype
+    actual_gradients = torch.autograd.grad(actual, actual_inputs, (grad_updated, grad_normalized))
+    expected_gradients = torch.autograd.grad(
+        expected, expected_inputs, (grad_updated, grad_normalized)
+    )
+    torch.testing.assert_close(actual_gradients[0], expected_gradients[0], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(
+        actual_gradients[1].float(), expected_gradients[1].float(), rtol=2e-3, atol=1e-5
+    )
+    for mine, theirs in zip(actual_gradients[2:], expected_gradients[2:]):
+        torch.testing.assert_close(mine, theirs, rtol=1e-4, atol=2e-4)
+
+
+def test_narrow_normalized_with_dropout_only_normalized_used_and_auto_route(recwarn):
+    torch.manual_seed(269)
+    x, branch, weight, bias = random_inputs(33, 512, branch_dtype=torch.bfloat16)
+    inputs = leaves((x, branch, weight, bias))
+    state = torch.cuda.get_rng_state()
+    updated, normalized = residual_layer_norm(
+        *inputs, dropout_p=0.2, normalized_dtype=torch.bfloat16
+    )
+    assert not [w for w in recwarn.list if issubclass(w.category, RuntimeWarning)]
+    torch.cuda.set_rng_state(state)
+    reference = residual_layer_norm(x, branch, weight, bias, dropout_p=0.2)
+    # same mask, same float32 arithmetic: the 16-bit output is the cast of the float32 one
+    assert torch.equal(updated, reference[0])
+    assert torch.equal(normalized, reference[1].to(torch.bfloat16))
+    gradients = torch.autograd.grad(normalized.float().square().sum(), inputs)
+    assert gradients[1].dtype == torch.bfloat16
+    assert all(torch.isfinite(g.float()).all() for g in gradients)
+
+
+def test_narrow_normalized_in_the_module():
+    from gfx1010_kernels.modules import ResidualLayerNorm
+
+    module = ResidualLayerNorm(
+        768, dropout_p=0.1, implementation="gfx1010", normalized_dtype=torch.bfloat16
+    ).cuda()
+    x = torch.randn(4, 9, 768, device=DEVICE, requires_grad=True)
+    branch = torch.randn(4, 9, 768, device=DEVICE, dtype=torch.bfloat16, requires_grad=True)
+    updated, normalized = module(x, branch)
+    assert normalized.dtype == torch.bfloat16
+    projection = torch.randn(768, 64, device=DEVICE, dtype=torch.bfloat16)
+    ((normalized @ projection).float().square().mean() + updated.mean()).backward()
+    assert module.weight.grad is not None and module.weight.grad.dtype == torch.float32
+    assert branch.grad.dtype == torch.bfloat16 and x.grad.dtype == torch.float32
