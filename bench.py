@@ -325,8 +325,7 @@ def run_native_arm(args, rank, local_rank, world):
     rows, hidden, branch_dtype, dropout_p, normalized_dtype = workload(args.workload)
     branch_bytes = 4 if branch_dtype == torch.float32 else 2
     normalized_bytes = 4 if normalized_dtype == torch.float32 else 2
-    # the host-buffer pipeline moves a float32 `normalized`: no end-to-end leg otherwise
-    skip_e2e = args.kernel_only or normalized_dtype != torch.float32
+    skip_e2e = args.kernel_only
     host = draw_inputs(rows, hidden, branch_dtype, seed=rank)
     x, branch, weight, bias, grad_updated, grad_normalized = (t.to(device) for t in host)
     grad_normalized = grad_normalized.to(normalized_dtype)
@@ -473,7 +472,8 @@ def run_native_arm(args, rank, local_rank, world):
         e2e = {"ms": float("nan"), "public_ms": float("nan"), "steps": 0, "h2d": 0, "d2h": 0}
     else:
         e2e = run_end_to_end(
-            args, device, host, weight, bias, dropout_p, world, residual_layer_norm
+            args, device, host, weight, bias, dropout_p, world, residual_layer_norm,
+            normalized_dtype,
         )
     sampler.stop()
 
@@ -577,7 +577,8 @@ def run_native_arm(args, rank, local_rank, world):
     return 0
 
 
-def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_layer_norm):
+def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_layer_norm,
+                   normalized_dtype=torch.float32):
     """The same step with host buffers on both sides, two ways:
 
     ``pipeline``    one C-ABI call (rln_sm100_host_forward_backward through
@@ -592,9 +593,12 @@ def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_
 
     from gfx1010_kernels.host_pipeline import HostPipeline
 
+    host = list(host)
+    host[5] = host[5].to(normalized_dtype)
     x_h, branch_h, weight_h, bias_h, gu_h, gy_h = (t.pin_memory() for t in host)
     rows, hidden = x_h.shape
-    pipeline = HostPipeline(hidden, branch_h.dtype, chunk_rows=8192, depth=3, device=device)
+    pipeline = HostPipeline(hidden, branch_h.dtype, chunk_rows=8192, depth=3, device=device,
+                            normalized_dtype=normalized_dtype)
     outputs = pipeline.allocate_outputs(x_h.shape)
     out_updated, out_normalized, out_grad_x, out_grad_branch, out_grad_params = outputs
     weight_leaf = weight.detach().clone().requires_grad_(True)
@@ -621,7 +625,8 @@ def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_
         grad_updated = gu_h.to(device, non_blocking=True)
         grad_normalized = gy_h.to(device, non_blocking=True)
         updated, normalized = residual_layer_norm(
-            x, branch, weight_leaf, bias_leaf, dropout_p, EPS, True, implementation="gfx1010"
+            x, branch, weight_leaf, bias_leaf, dropout_p, EPS, True, implementation="gfx1010",
+            normalized_dtype=normalized_dtype,
         )
         grad_x, grad_branch, grad_weight, grad_bias = torch.autograd.grad(
             (updated, normalized), (x, branch, weight_leaf, bias_leaf),

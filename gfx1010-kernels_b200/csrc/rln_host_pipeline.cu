@@ -31,9 +31,9 @@ struct Slot {
     float* x = nullptr;
     void* branch = nullptr;
     float* grad_updated = nullptr;
-    float* grad_normalized = nullptr;
+    void* grad_normalized = nullptr;
     float* updated = nullptr;
-    float* normalized = nullptr;
+    void* normalized = nullptr;
     float* grad_x = nullptr;
     void* grad_branch = nullptr;
     float* mean = nullptr;
@@ -53,6 +53,7 @@ struct RlnHostPipeline {
     int device = 0;
     int32_t hidden = 0;
     int32_t branch_dtype = 0;
+    int32_t normalized_dtype = 0;
     int64_t chunk_rows = 0;
     int32_t depth = 0;
     int64_t workspace_bytes = 0;
@@ -108,7 +109,8 @@ void release(RlnHostPipeline* p) {
 
 bool allocate(RlnHostPipeline* p) {
     const size_t elements = static_cast<size_t>(p->chunk_rows) * p->hidden;
-    const size_t branch_bytes = elements * (p->branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2);
+    const size_t branch_bytes = elements * (p->branch_dtype == RLN_DTYPE_FLOAT32 ? 4 : 2);
+    const size_t normalized_bytes = elements * (p->normalized_dtype == RLN_DTYPE_FLOAT32 ? 4 : 2);
     RLN_TRY(cudaStreamCreateWithFlags(&p->stream_in, cudaStreamNonBlocking));
     RLN_TRY(cudaStreamCreateWithFlags(&p->stream_compute, cudaStreamNonBlocking));
     RLN_TRY(cudaStreamCreateWithFlags(&p->stream_out, cudaStreamNonBlocking));
@@ -120,9 +122,9 @@ bool allocate(RlnHostPipeline* p) {
         RLN_TRY(cudaMalloc(&slot.x, elements * 4));
         RLN_TRY(cudaMalloc(&slot.branch, branch_bytes));
         RLN_TRY(cudaMalloc(&slot.grad_updated, elements * 4));
-        RLN_TRY(cudaMalloc(&slot.grad_normalized, elements * 4));
+        RLN_TRY(cudaMalloc(&slot.grad_normalized, normalized_bytes));
         RLN_TRY(cudaMalloc(&slot.updated, elements * 4));
-        RLN_TRY(cudaMalloc(&slot.normalized, elements * 4));
+        RLN_TRY(cudaMalloc(&slot.normalized, normalized_bytes));
         RLN_TRY(cudaMalloc(&slot.grad_x, elements * 4));
         RLN_TRY(cudaMalloc(&slot.grad_branch, branch_bytes));
         RLN_TRY(cudaMalloc(&slot.mean, p->chunk_rows * sizeof(float)));
@@ -145,6 +147,7 @@ extern "C" int rln_sm100_host_pipeline_create(
     RlnHostPipeline** pipeline,
     int32_t hidden,
     int32_t branch_dtype,
+    int32_t normalized_dtype,
     int64_t chunk_rows,
     int32_t depth) {
     if (pipeline == nullptr) {
@@ -154,9 +157,13 @@ extern "C" int rln_sm100_host_pipeline_create(
     if (chunk_rows <= 0 || chunk_rows > (1 << 24) || depth < 2 || depth > kMaxDepth) {
         return RLN_ERR_HOST_BUFFERS;
     }
-    if (branch_dtype != RLN_BRANCH_FLOAT32 && branch_dtype != RLN_BRANCH_FLOAT16
-        && branch_dtype != RLN_BRANCH_BFLOAT16) {
+    if (branch_dtype != RLN_DTYPE_FLOAT32 && branch_dtype != RLN_DTYPE_FLOAT16
+        && branch_dtype != RLN_DTYPE_BFLOAT16) {
         return RLN_ERR_BRANCH_DTYPE;
+    }
+    if (normalized_dtype != RLN_DTYPE_FLOAT32 && normalized_dtype != RLN_DTYPE_FLOAT16
+        && normalized_dtype != RLN_DTYPE_BFLOAT16) {
+        return RLN_ERR_NORMALIZED_DTYPE;
     }
     // the deterministic workspace for the largest chunk; also validates hidden
     const int64_t workspace_bytes = rln_sm100_backward_workspace_bytes(chunk_rows, hidden, 1);
@@ -174,6 +181,7 @@ extern "C" int rln_sm100_host_pipeline_create(
     }
     p->hidden = hidden;
     p->branch_dtype = branch_dtype;
+    p->normalized_dtype = normalized_dtype;
     p->chunk_rows = chunk_rows;
     p->depth = depth;
     p->workspace_bytes = workspace_bytes;
@@ -216,9 +224,9 @@ int enqueue_step(
     const float* weight,
     const float* bias,
     const float* grad_updated,
-    const float* grad_normalized,
+    const void* grad_normalized,
     float* updated,
-    float* normalized,
+    void* normalized,
     float* grad_x,
     void* grad_branch,
     float* grad_parameters,
@@ -251,9 +259,12 @@ int enqueue_step(
         return RLN_ERR_HOST_BUFFERS;
     }
     const int64_t hidden = p->hidden;
-    const size_t branch_element = p->branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2;
+    const size_t branch_element = p->branch_dtype == RLN_DTYPE_FLOAT32 ? 4 : 2;
+    const size_t normalized_element = p->normalized_dtype == RLN_DTYPE_FLOAT32 ? 4 : 2;
     const char* branch_bytes = static_cast<const char*>(branch);
     char* grad_branch_bytes = static_cast<char*>(grad_branch);
+    const char* grad_normalized_bytes = static_cast<const char*>(grad_normalized);
+    char* normalized_bytes = static_cast<char*>(normalized);
 
     for (int s = 0; s < p->depth; ++s) {
         p->slots[s].used = false;
@@ -283,8 +294,8 @@ int enqueue_step(
             slot.grad_updated, grad_updated + first, elements * 4, cudaMemcpyHostToDevice,
             p->stream_in));
         RLN_TRY(cudaMemcpyAsync(
-            slot.grad_normalized, grad_normalized + first, elements * 4, cudaMemcpyHostToDevice,
-            p->stream_in));
+            slot.grad_normalized, grad_normalized_bytes + first * normalized_element,
+            elements * normalized_element, cudaMemcpyHostToDevice, p->stream_in));
         RLN_TRY(cudaEventRecord(slot.in_ready, p->stream_in));
 
         // compute (the slot's outputs are free once its previous results left)
@@ -294,7 +305,7 @@ int enqueue_step(
         }
         int status = rln_sm100_forward(
             slot.x, slot.branch, p->weight, p->bias, slot.updated, slot.normalized, slot.mean,
-            slot.rstd, slot.mask, count, p->hidden, p->branch_dtype, RLN_DTYPE_FLOAT32,
+            slot.rstd, slot.mask, count, p->hidden, p->branch_dtype, p->normalized_dtype,
             dropout_active, dropout_p, eps, seed, offset, row_base + begin, p->stream_compute);
         if (status != RLN_OK) {
             return status;
@@ -303,7 +314,7 @@ int enqueue_step(
             slot.grad_updated, slot.grad_normalized, slot.updated, p->weight, slot.mean,
             slot.rstd, slot.mask, slot.grad_x, slot.grad_branch, slot.grad_parameters,
             slot.workspace, p->workspace_bytes, count, p->hidden, p->branch_dtype,
-            RLN_DTYPE_FLOAT32, dropout_active, dropout_p, deterministic, p->stream_compute);
+            p->normalized_dtype, dropout_active, dropout_p, deterministic, p->stream_compute);
         if (status != RLN_OK) {
             return status;
         }
@@ -318,8 +329,8 @@ int enqueue_step(
         RLN_TRY(cudaMemcpyAsync(
             updated + first, slot.updated, elements * 4, cudaMemcpyDeviceToHost, p->stream_out));
         RLN_TRY(cudaMemcpyAsync(
-            normalized + first, slot.normalized, elements * 4, cudaMemcpyDeviceToHost,
-            p->stream_out));
+            normalized_bytes + first * normalized_element, slot.normalized,
+            elements * normalized_element, cudaMemcpyDeviceToHost, p->stream_out));
         RLN_TRY(cudaMemcpyAsync(
             grad_x + first, slot.grad_x, elements * 4, cudaMemcpyDeviceToHost, p->stream_out));
         RLN_TRY(cudaMemcpyAsync(
@@ -343,9 +354,9 @@ extern "C" int rln_sm100_host_forward_backward(
     const float* weight,
     const float* bias,
     const float* grad_updated,
-    const float* grad_normalized,
+    const void* grad_normalized,
     float* updated,
-    float* normalized,
+    void* normalized,
     float* grad_x,
     void* grad_branch,
     float* grad_parameters,

@@ -24,7 +24,7 @@ _LIBRARY_PATH = Path(__file__).resolve().parent / "librln_sm100.so"
 _library = None
 
 _ptr = ctypes.c_void_p
-# RLN_BRANCH_FLOAT32 / FLOAT16 / BFLOAT16 of include/rln_sm100.h
+# RLN_DTYPE_FLOAT32 / FLOAT16 / BFLOAT16 of include/rln_sm100.h (branch and normalized)
 _BRANCH_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 
@@ -38,7 +38,8 @@ def _load():
         lib.rln_sm100_status_string.argtypes = [ctypes.c_int]
         lib.rln_sm100_host_pipeline_create.restype = ctypes.c_int
         lib.rln_sm100_host_pipeline_create.argtypes = [
-            ctypes.POINTER(_ptr), ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32,
+            ctypes.POINTER(_ptr), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+            ctypes.c_int64, ctypes.c_int32,
         ]
         lib.rln_sm100_host_pipeline_destroy.restype = ctypes.c_int
         lib.rln_sm100_host_pipeline_destroy.argtypes = [_ptr]
@@ -59,22 +60,30 @@ def _check(status, what):
 
 
 class HostPipeline:
-    """Device staging buffers, streams and events for one (hidden, branch dtype).
+    """Device staging buffers, streams and events for one (hidden, branch dtype,
+    normalized dtype).
 
     ``chunk_rows`` rows are in flight per stage and ``depth`` chunks are
     buffered (device memory: about ``depth * chunk_rows * hidden * 30`` bytes).
+    ``normalized_dtype`` is the type of ``normalized`` and ``grad_normalized``
+    (float32 by default; float16 / bfloat16 move 2 bytes less per element in
+    each direction over the PCIe link that bounds this step).
     One call at a time per pipeline.
     """
 
-    def __init__(self, hidden, branch_dtype=torch.float16, chunk_rows=8192, depth=3, device=None):
+    def __init__(self, hidden, branch_dtype=torch.float16, chunk_rows=8192, depth=3, device=None,
+                 normalized_dtype=torch.float32):
         if not torch.cuda.is_available():
             raise RuntimeError("HostPipeline needs a CUDA device; there is no CPU fallback")
         if branch_dtype not in _BRANCH_CODES:
             raise ValueError("branch must use float16, bfloat16 or float32")
+        if normalized_dtype not in _BRANCH_CODES:
+            raise ValueError("normalized must use float16, bfloat16 or float32")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
             else torch.device(device)
         self.hidden = int(hidden)
         self.branch_dtype = branch_dtype
+        self.normalized_dtype = normalized_dtype
         self.chunk_rows = int(chunk_rows)
         self.depth = int(depth)
         self._handle = _ptr()
@@ -82,7 +91,8 @@ class HostPipeline:
             torch.cuda.current_stream()  # make sure the device's context exists
             status = _load().rln_sm100_host_pipeline_create(
                 ctypes.byref(self._handle), self.hidden,
-                _BRANCH_CODES[branch_dtype], self.chunk_rows, self.depth,
+                _BRANCH_CODES[branch_dtype], _BRANCH_CODES[normalized_dtype],
+                self.chunk_rows, self.depth,
             )
         _check(status, "rln_sm100_host_pipeline_create")
 
@@ -111,7 +121,7 @@ class HostPipeline:
 
         return (
             host(shape, torch.float32),
-            host(shape, torch.float32),
+            host(shape, self.normalized_dtype),
             host(shape, torch.float32),
             host(shape, self.branch_dtype),
             host((2, self.hidden), torch.float32),
@@ -146,9 +156,10 @@ class HostPipeline:
         tensors = (x, branch, weight, bias, grad_updated, grad_normalized)
         if any(t.is_cuda for t in tensors):
             raise RuntimeError("HostPipeline takes host tensors; use residual_layer_norm for device tensors")
-        if x.dtype != torch.float32 or grad_updated.dtype != torch.float32 \
-                or grad_normalized.dtype != torch.float32:
-            raise RuntimeError("x and the upstream gradients must use float32")
+        if x.dtype != torch.float32 or grad_updated.dtype != torch.float32:
+            raise RuntimeError("x and grad_updated must use float32")
+        if grad_normalized.dtype != self.normalized_dtype:
+            raise RuntimeError(f"grad_normalized must use {self.normalized_dtype}")
         if branch.dtype != self.branch_dtype:
             raise RuntimeError(f"branch must use {self.branch_dtype}")
         if weight.dtype != torch.float32 or bias.dtype != torch.float32:
@@ -166,6 +177,8 @@ class HostPipeline:
         if out is None:
             out = self.allocate_outputs(x.shape)
         updated, normalized, grad_x, grad_branch, grad_parameters = out
+        if normalized.dtype != self.normalized_dtype or grad_branch.dtype != self.branch_dtype:
+            raise RuntimeError("the output tensors do not have the pipeline's dtypes")
         rows = x.numel() // self.hidden
         active = bool(training and dropout_p > 0.0)
         with torch.cuda.device(self.device):

@@ -22,7 +22,8 @@ from typing import Callable, Optional, Tuple
 import torch
 
 
-# the extension's branch type codes: False/0 float32, True/1 float16, 2 bfloat16
+# the extension's element type codes (branch and normalized): False/0 float32,
+# True/1 float16, 2 bfloat16
 _BRANCH_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 
@@ -51,7 +52,11 @@ class ShardedStepResult:
 
 def _native_forward_backward(x, branch, weight, bias, grad_updated, grad_normalized,
                              dropout_p, eps, training, seed, offset, row_base):
-    """Forward + backward of one shard through the raw extension entries."""
+    """Forward + backward of one shard through the raw extension entries.
+
+    ``normalized`` is produced in the type of ``grad_normalized`` (float32, or
+    float16 / bfloat16 for a consumer that takes it in half precision).
+    """
     from ._normalization_native import _extension
 
     extension, reason = _extension()
@@ -59,7 +64,7 @@ def _native_forward_backward(x, branch, weight, bias, grad_updated, grad_normali
         raise RuntimeError(f"gfx1010 native extension is unavailable: {reason}")
     updated, normalized, mean, rstd, mask = extension.residual_layer_norm_forward_seeded(
         x, branch, weight, bias, float(dropout_p), float(eps), bool(training), 128,
-        int(seed), int(offset), int(row_base),
+        int(seed), int(offset), int(row_base), _BRANCH_CODES[grad_normalized.dtype],
     )
     grad_x, grad_branch, grad_weight, grad_bias = extension.residual_layer_norm_backward(
         grad_updated, grad_normalized, updated, weight, mean, rstd, mask,
@@ -105,6 +110,8 @@ def sharded_forward_backward(
     if x_shard.shape != branch_shard.shape or x_shard.shape != grad_updated_shard.shape \
             or x_shard.shape != grad_normalized_shard.shape:
         raise ValueError("the shard's tensors must have the same shape")
+    if grad_normalized_shard.dtype not in _BRANCH_CODES:
+        raise ValueError("grad_normalized must use float32, float16 or bfloat16")
     compute = compute or _native_forward_backward
     updated, normalized, grad_x, grad_branch, parameters, mask = compute(
         x_shard, branch_shard, weight, bias, grad_updated_shard, grad_normalized_shard,

@@ -323,6 +323,10 @@ RLN_API int rln_sm100_backward_static_scratch(
  *   updated, normalized, grad_x, grad_branch    host out, [rows, hidden]
  *   grad_parameters                             host out, float32 [2, hidden]
  *   other arguments as in rln_sm100_forward / rln_sm100_backward.
+ * branch / grad_branch have the pipeline's branch_dtype, normalized /
+ * grad_normalized its normalized_dtype (RLN_DTYPE_*); the step is bound by the
+ * PCIe link, so a 16-bit `normalized` shortens it by the bytes it saves
+ * (2 of 14 per element in each direction).
  */
 typedef struct RlnHostPipeline RlnHostPipeline;
 
@@ -330,6 +334,7 @@ RLN_API int rln_sm100_host_pipeline_create(
     RlnHostPipeline** pipeline,
     int32_t hidden,
     int32_t branch_dtype,
+    int32_t normalized_dtype,
     int64_t chunk_rows,
     int32_t depth);
 
@@ -342,9 +347,9 @@ RLN_API int rln_sm100_host_forward_backward(
     const float* weight,
     const float* bias,
     const float* grad_updated,
-    const float* grad_normalized,
+    const void* grad_normalized,
     float* updated,
-    float* normalized,
+    void* normalized,
     float* grad_x,
     void* grad_branch,
     float* grad_parameters,

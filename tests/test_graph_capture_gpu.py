@@ -41,12 +41,17 @@ def _warm_up(function):
     torch.cuda.synchronize()
 
 
-@pytest.mark.parametrize("hidden", [128, 768])
-def test_captured_forward_draws_the_mask_of_the_generator_state_at_replay(capture_allowed, hidden):
+@pytest.mark.parametrize(
+    "hidden,normalized_dtype",
+    [(128, None), (768, None), (256, torch.bfloat16), (1024, torch.float16)],
+)
+def test_captured_forward_draws_the_mask_of_the_generator_state_at_replay(
+        capture_allowed, hidden, normalized_dtype):
     inputs = _inputs(64, hidden)
 
     def forward():
-        return residual_layer_norm(*inputs, dropout_p=0.5, implementation="gfx1010")
+        return residual_layer_norm(*inputs, dropout_p=0.5, implementation="gfx1010",
+                                   normalized_dtype=normalized_dtype)
 
     _warm_up(forward)
     graph = torch.cuda.CUDAGraph()

@@ -13,22 +13,26 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize(
-    "rows,hidden,branch_dtype,chunk_rows,depth,deterministic",
+    "rows,hidden,branch_dtype,chunk_rows,depth,deterministic,normalized_dtype",
     [
-        (1000, 768, torch.float16, 128, 2, False),
-        (1000, 768, torch.float16, 128, 3, True),
-        (257, 128, torch.float32, 100, 2, True),
-        (64, 1024, torch.float16, 4096, 2, False),   # single partial chunk
-        (4101, 256, torch.float32, 512, 4, False),
-        (777, 512, torch.bfloat16, 256, 3, True),
+        (1000, 768, torch.float16, 128, 2, False, torch.float32),
+        (1000, 768, torch.float16, 128, 3, True, torch.float32),
+        (257, 128, torch.float32, 100, 2, True, torch.float32),
+        (64, 1024, torch.float16, 4096, 2, False, torch.float32),   # single partial chunk
+        (4101, 256, torch.float32, 512, 4, False, torch.float32),
+        (777, 512, torch.bfloat16, 256, 3, True, torch.float32),
+        (1000, 768, torch.float16, 128, 3, False, torch.bfloat16),
+        (515, 384, torch.bfloat16, 200, 2, True, torch.float16),
     ],
 )
 def test_host_pipeline_matches_device_calls(rows, hidden, branch_dtype, chunk_rows, depth,
-                                            deterministic):
-    host = draw_inputs((rows,), hidden, branch_dtype, seed=rows, device="cpu")
+                                            deterministic, normalized_dtype):
+    host = list(draw_inputs((rows,), hidden, branch_dtype, seed=rows, device="cpu"))
+    host[5] = host[5].to(normalized_dtype)
     x, branch, weight, bias, grad_updated, grad_normalized = (t.pin_memory() for t in host)
     dropout_p, eps, seed, offset, row_base = 0.1, 1e-5, 77, 12, 5000
-    with HostPipeline(hidden, branch_dtype, chunk_rows=chunk_rows, depth=depth) as pipeline:
+    with HostPipeline(hidden, branch_dtype, chunk_rows=chunk_rows, depth=depth,
+                      normalized_dtype=normalized_dtype) as pipeline:
         out = pipeline.forward_backward(
             x, branch, weight, bias, grad_updated, grad_normalized, dropout_p, eps, True,
             seed=seed, offset=offset, row_base=row_base, deterministic=deterministic,
@@ -40,7 +44,7 @@ def test_host_pipeline_matches_device_calls(rows, hidden, branch_dtype, chunk_ro
     device = [t.cuda() for t in host]
     status, updated, normalized, mean, rstd, mask = cabi.forward(
         device[0], device[1], device[2], device[3], dropout_p, eps, True,
-        seed=seed, offset=offset, row_base=row_base,
+        seed=seed, offset=offset, row_base=row_base, normalized_dtype=normalized_dtype,
     )
     assert status == 0
     status, grad_x, grad_branch, grad_parameters = cabi.backward(
@@ -49,6 +53,7 @@ def test_host_pipeline_matches_device_calls(rows, hidden, branch_dtype, chunk_ro
     )
     assert status == 0
     torch.cuda.synchronize()
+    assert out[1].dtype == normalized_dtype
     assert torch.equal(out[0], updated.cpu())
     assert torch.equal(out[1], normalized.cpu())
     assert torch.equal(out[2], grad_x.cpu())
@@ -85,6 +90,9 @@ def test_host_pipeline_rejects_bad_arguments():
         x = torch.zeros(4, 128)
         with pytest.raises(RuntimeError, match="branch must use"):
             pipeline.forward_backward(x, x, torch.ones(128), torch.zeros(128), x, x)
+        with pytest.raises(RuntimeError, match="grad_normalized must use"):
+            pipeline.forward_backward(
+                x, x.half(), torch.ones(128), torch.zeros(128), x, x.bfloat16())
         with pytest.raises(RuntimeError, match="host tensors"):
             pipeline.forward_backward(x.cuda(), x.half(), torch.ones(128), torch.zeros(128), x, x)
         with pytest.raises(RuntimeError, match=r"dropout_p must be in \[0, 1\)"):

@@ -11,12 +11,17 @@ from gfx1010_kernels.sharded import shard_bounds, sharded_forward_backward
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("world", [2, 3, 8])
-def test_native_shards_reproduce_the_unsharded_step(world):
+@pytest.mark.parametrize(
+    "world,normalized_dtype",
+    [(2, torch.float32), (3, torch.float32), (8, torch.float32), (3, torch.bfloat16)],
+)
+def test_native_shards_reproduce_the_unsharded_step(world, normalized_dtype):
     rows, hidden = 1001, 768
     x, branch, weight, bias, grad_updated, grad_normalized = draw_inputs(
         (rows,), hidden, torch.float16, 21
     )
+    # `normalized` comes back in the type its gradient is given in
+    grad_normalized = grad_normalized.to(normalized_dtype)
     arguments = dict(dropout_p=0.1, eps=1e-5, training=True, seed=5, offset=16)
     whole = sharded_forward_backward(
         x, branch, weight, bias, grad_updated, grad_normalized, row_base=0, **arguments
@@ -33,6 +38,7 @@ def test_native_shards_reproduce_the_unsharded_step(world):
         total_weight += piece.grad_weight.double()
         total_bias += piece.grad_bias.double()
         pieces.append(piece)
+    assert whole.normalized.dtype == normalized_dtype
     for name in ("updated", "normalized", "grad_x", "grad_branch", "mask"):
         joined = torch.cat([getattr(piece, name) for piece in pieces])
         assert torch.equal(joined, getattr(whole, name)), name
