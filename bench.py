@@ -318,8 +318,18 @@ def run_native_arm(args, rank, local_rank, world):
     if world > 1:
         # a short timeout: a rank that stops calling collectives must surface as an
         # error within minutes, not hold the GPUs for the default ten
+        # NCCL on a high-priority stream: the all-reduce of step i is launched
+        # while the forward of step i+1 already fills every SM with short CTAs;
+        # at equal priority its CTAs are placed only after the forward's grid has
+        # been handed out, i.e. at the forward's tail, and part of its latency
+        # shows.  With priority it takes the first slots that free up.
+        options = None
+        if not args.default_priority_collectives:
+            options = dist.ProcessGroupNCCL.Options()
+            options.is_high_priority_stream = True
         dist.init_process_group(
-            "nccl", device_id=device, timeout=datetime.timedelta(seconds=120)
+            "nccl", device_id=device, timeout=datetime.timedelta(seconds=120),
+            pg_options=options,
         )
 
     rows, hidden, branch_dtype, dropout_p, normalized_dtype = workload(args.workload)
@@ -671,6 +681,8 @@ def main(argv=None):
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="h768_64Mi")
+    parser.add_argument("--default-priority-collectives", action="store_true",
+                        help="N > 1: run NCCL on a default-priority stream (A/B switch)")
     parser.add_argument(
         "--kernel-events-in-loop",
         action="store_true",

@@ -10,6 +10,14 @@ needs exactly two things beyond the single-GPU calls:
 * one all-reduce (sum) of the contiguous ``[2, hidden]`` parameter-gradient
   buffer after the backward.
 
+Overlap: the all-reduce may run under the NEXT step's forward but should be
+finished before that step's backward is launched (the backward's persistent
+grid fills every SM exactly once; a resident communication kernel splits it
+into two waves).  Create the NCCL group with a high-priority stream
+(``ProcessGroupNCCL.Options.is_high_priority_stream = True``), otherwise the
+collective is scheduled behind the forward's queued CTAs and its latency shows
+(measured on 8 GPUs: 7.41x -> 7.91x of one GPU).
+
 The reference project is single-device and has no counterpart of this module;
 it sits on the caller side of the path.  The collective goes through
 ``torch.distributed`` (NCCL over NVLink/NVSwitch between GPUs; any backend
