@@ -294,9 +294,10 @@ def workload_config(name, gpus):
         "eps": EPS,
         "training": True,
         "parameter_gradients": "atomic (non-deterministic mode)",
-        "parallelism": f"rows sharded over {gpus} GPU(s); NCCL all-reduce of the [2,H] grads, "
-                       "asynchronous (overlaps the next step's forward, waited for before "
-                       "that step's backward, inside the timed region)" if gpus > 1
+        "parallelism": f"rows sharded over {gpus} GPU(s); NCCL all-reduce of the [2,H] grads on a "
+                       "high-priority stream, asynchronous (overlaps the next step's forward, "
+                       "waited for before that step's backward, inside the timed region)"
+        if gpus > 1
         else "1 GPU",
         "l2": "inputs larger than L2 (no flush needed)" if rows * hidden * 4 > 126e6
         else "flushed between steps (256 MB written, then read)",
