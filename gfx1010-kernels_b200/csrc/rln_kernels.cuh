@@ -283,6 +283,7 @@ struct BranchIO<float> {
         store_f4<kAligned, kStream>(static_cast<float*>(base), chunk, v);
     }
     static __device__ __forceinline__ float round(float v) { return v; }
+    static __device__ __forceinline__ float4 round4(float4 v) { return v; }
 };
 
 template <>
@@ -324,6 +325,12 @@ struct BranchIO<__half> {
     }
     static __device__ __forceinline__ float round(float v) {
         return __half2float(__float2half_rn(v));
+    }
+    // four values through float16 and back: two packed conversions down, two up
+    static __device__ __forceinline__ float4 round4(float4 v) {
+        const float2 lo = __half22float2(__floats2half2_rn(v.x, v.y));
+        const float2 hi = __half22float2(__floats2half2_rn(v.z, v.w));
+        return make_float4(lo.x, lo.y, hi.x, hi.y);
     }
 };
 
@@ -374,6 +381,15 @@ struct BranchIO<__nv_bfloat16> {
     static __device__ __forceinline__ float round(float v) {
         return __bfloat162float(__float2bfloat16_rn(v));
     }
+    static __device__ __forceinline__ float4 round4(float4 v) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
+        const uint32_t a = *reinterpret_cast<const uint32_t*>(&lo);
+        const uint32_t b = *reinterpret_cast<const uint32_t*>(&hi);
+        return make_float4(
+            __uint_as_float(a << 16), __uint_as_float(a & 0xffff0000u),
+            __uint_as_float(b << 16), __uint_as_float(b & 0xffff0000u));
+    }
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -384,14 +400,20 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// dropped = round_to_branch(float(b) * keep * scale): two separate fp32
-// multiplies (no contraction) so the result is bit-identical to the torch
-// decomposition evaluated with the same mask.
+// dropped = round_to_branch(float(b) * keep * scale) for the four columns of a
+// chunk; `nibble` holds their keep bits.  One multiply by (keep ? scale : 0)
+// gives the same bits as the two multiplies of the torch decomposition
+// evaluated with this mask -- b * 1 * scale == b * scale and
+// b * 0 * scale == b * 0 including the sign of zero, and a non-finite b times
+// zero is NaN either way -- and the sum is never contracted into an fma.
 template <typename BranchT>
-__device__ __forceinline__ float drop_one(float b, bool keep, float scale) {
-    // A select (keep ? round(b * scale) : 0) saves a multiply but measured no
-    // faster on B200: the forward is not issue-bound.
-    return BranchIO<BranchT>::round(__fmul_rn(__fmul_rn(b, keep ? 1.0f : 0.0f), scale));
+__device__ __forceinline__ float4 drop_four(float4 b, uint32_t nibble, float scale) {
+    float4 dropped;
+    dropped.x = __fmul_rn(b.x, (nibble & 1u) ? scale : 0.0f);
+    dropped.y = __fmul_rn(b.y, (nibble & 2u) ? scale : 0.0f);
+    dropped.z = __fmul_rn(b.z, (nibble & 4u) ? scale : 0.0f);
+    dropped.w = __fmul_rn(b.w, (nibble & 8u) ? scale : 0.0f);
+    return BranchIO<BranchT>::round4(dropped);
 }
 
 // ---------------------------------------------------------------------------
@@ -482,11 +504,7 @@ rln_forward_kernel(const ForwardParams p) {
             for (int k = 0; k < V; ++k) {
                 float4 dropped = b[r][k];
                 if constexpr (kDropout) {
-                    const uint32_t n = nibble[r][k];
-                    dropped.x = drop_one<BranchT>(dropped.x, n & 1u, p.scale);
-                    dropped.y = drop_one<BranchT>(dropped.y, n & 2u, p.scale);
-                    dropped.z = drop_one<BranchT>(dropped.z, n & 4u, p.scale);
-                    dropped.w = drop_one<BranchT>(dropped.w, n & 8u, p.scale);
+                    dropped = drop_four<BranchT>(dropped, nibble[r][k], p.scale);
                 }
                 float4 value = u[r][k];
                 value.x = __fadd_rn(value.x, dropped.x);
@@ -629,11 +647,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
         for (int k = 0; k < V; ++k) {
             float4 dropped = b[k];
             if constexpr (kDropout) {
-                const uint32_t n = nibble[k];
-                dropped.x = drop_one<BranchT>(dropped.x, n & 1u, p.scale);
-                dropped.y = drop_one<BranchT>(dropped.y, n & 2u, p.scale);
-                dropped.z = drop_one<BranchT>(dropped.z, n & 4u, p.scale);
-                dropped.w = drop_one<BranchT>(dropped.w, n & 8u, p.scale);
+                dropped = drop_four<BranchT>(dropped, nibble[k], p.scale);
             }
             float4 value = u[k];
             value.x = __fadd_rn(value.x, dropped.x);
@@ -826,10 +840,11 @@ rln_backward_kernel(const BackwardParams p) {
                 store_f4<kAligned, kStreamHints>(p.grad_x, chunk, total);
                 if constexpr (kDropout) {
                     const uint32_t n = words[r][k] >> (4 * (lane & 7));
-                    total.x = __fmul_rn(__fmul_rn(total.x, (n & 1u) ? 1.0f : 0.0f), p.scale);
-                    total.y = __fmul_rn(__fmul_rn(total.y, (n & 2u) ? 1.0f : 0.0f), p.scale);
-                    total.z = __fmul_rn(__fmul_rn(total.z, (n & 4u) ? 1.0f : 0.0f), p.scale);
-                    total.w = __fmul_rn(__fmul_rn(total.w, (n & 8u) ? 1.0f : 0.0f), p.scale);
+                    // g * keep * scale as one multiply (same bits, see drop_four)
+                    total.x = __fmul_rn(total.x, (n & 1u) ? p.scale : 0.0f);
+                    total.y = __fmul_rn(total.y, (n & 2u) ? p.scale : 0.0f);
+                    total.z = __fmul_rn(total.z, (n & 4u) ? p.scale : 0.0f);
+                    total.w = __fmul_rn(total.w, (n & 8u) ? p.scale : 0.0f);
                 }
                 IO::template store<kAligned, kStreamHints>(p.grad_branch, chunk, total);
             }
