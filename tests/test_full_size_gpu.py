@@ -262,3 +262,43 @@ def test_more_than_2_to_the_31_elements_is_indexed_with_64_bits():
     assert torch.equal(whole[2][begin:], part[2])
     expected_bias = grad_normalized.sum(dim=0, dtype=torch.float64)
     assert_parameters_close(whole[3][1], expected_bias, rows, "grad_bias")
+
+
+@pytest.mark.parametrize(
+    "rows,hidden,branch_dtype,normalized_dtype",
+    [
+        (87381, 768, torch.float16, torch.bfloat16),
+        (87381, 768, torch.bfloat16, torch.float16),
+        (64 * 4096, 1024, torch.float16, torch.bfloat16),
+        (5 * 817, 256, torch.float32, torch.bfloat16),
+    ],
+)
+def test_full_size_16_bit_normalized_is_the_cast_of_the_float32_path(
+        rows, hidden, branch_dtype, normalized_dtype):
+    """The 16-bit `normalized` path is the float32 path with one rounding on
+    store and one widening on load, so at any size: every other forward output
+    is bit-identical, `normalized` is bit-identical to the cast of the float32
+    output, and the backward fed the 16-bit gradient is bit-identical to the
+    float32 backward fed the widened gradient (fixed-order mode)."""
+    x, branch, weight, bias, grad_updated, grad_normalized = device_inputs(
+        rows, hidden, branch_dtype, seed=rows % 97
+    )
+    p = 0.1
+    wide = cabi.forward(x, branch, weight, bias, p, 1e-5, True, seed=3, offset=8)
+    narrow = cabi.forward(x, branch, weight, bias, p, 1e-5, True, seed=3, offset=8,
+                          normalized_dtype=normalized_dtype)
+    assert wide[0] == narrow[0] == 0
+    for index in (1, 3, 4, 5):                       # updated, mean, rstd, mask
+        assert torch.equal(wide[index], narrow[index])
+    assert narrow[2].dtype == normalized_dtype
+    assert torch.equal(narrow[2], wide[2].to(normalized_dtype))
+
+    narrow_gradient = grad_normalized.to(normalized_dtype)
+    _, updated, _, mean, rstd, mask = wide
+    args = (updated, weight, mean, rstd, mask, p, True, branch_dtype, True)
+    from_narrow = cabi.backward(grad_updated, narrow_gradient, *args)
+    from_wide = cabi.backward(grad_updated, narrow_gradient.float(), *args)
+    assert from_narrow[0] == from_wide[0] == 0
+    torch.cuda.synchronize()
+    for a, b in zip(from_narrow[1:], from_wide[1:]):
+        assert torch.equal(a, b)
