@@ -442,6 +442,23 @@ def run_native_arm(args, rank, local_rank, world):
         warm(extra, warmup_actual)
         warmup_actual += extra
 
+    run_step = step
+    if args.cuda_graph:
+        if world > 1:
+            raise RuntimeError("--cuda-graph is a single-GPU mode")
+        # One step (forward, zeroing kernel, backward and the allocator's work)
+        # recorded once; every replay re-runs it with the recorded Philox offset.
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_outputs = step(warmup_actual, False)
+
+        def run_step(index, record):
+            graph.replay()
+            return graph_outputs
+
+        for _ in range(10):
+            run_step(0, False)
+
     fence()
     timed_begin = time.perf_counter()
     start = torch.cuda.Event(enable_timing=True)
@@ -455,7 +472,7 @@ def run_native_arm(args, rank, local_rank, world):
             begin_event = torch.cuda.Event(enable_timing=True)
             end_event = torch.cuda.Event(enable_timing=True)
             begin_event.record()
-        step(warmup_actual + index, args.kernel_events_in_loop)
+        run_step(warmup_actual + index, args.kernel_events_in_loop)
         if flush is not None:
             end_event.record()
             step_events.append((begin_event, end_event))
@@ -542,6 +559,8 @@ def run_native_arm(args, rank, local_rank, world):
             "dtype": "f32",
             "data": "synthetic",
             "config": workload_config(args.workload, world),
+            "launch": "one step recorded into a CUDA graph, replayed (fixed Philox offset)"
+            if args.cuda_graph else "eager (three launches per step through the extension)",
             "hbm_gbs_step": step_gbs,
             "hbm_frac_of_8000": step_gbs / (HBM_SPEC_GBS * world),
             "hbm_frac_of_measured": step_gbs / (peak * world),
@@ -685,6 +704,9 @@ def main(argv=None):
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="h768_64Mi")
+    parser.add_argument("--cuda-graph", action="store_true",
+                        help="N = 1: record one step into a CUDA graph and time its replays "
+                             "(what a caller does for launch-bound shapes)")
     parser.add_argument("--default-priority-collectives", action="store_true",
                         help="N > 1: run NCCL on a default-priority stream (A/B switch)")
     parser.add_argument(
