@@ -71,3 +71,18 @@ def test_reference_arm_prints_one_json_line():
         "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
     }
     assert record["gpu_launches"] == 0 and record["vs_baseline"] is None
+
+
+def test_reference_arm_under_torchrun_prints_on_rank_0_only():
+    completed = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+         "--master-addr", "127.0.0.1", "--master-port", "29631",
+         str(REPO / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+         "--warmup", "0", "--workload", "c2_5x817x256_fp32"],
+        capture_output=True, text=True, timeout=600, check=True,
+    )
+    lines = [line for line in completed.stdout.splitlines() if line.startswith("{")]
+    assert len(lines) == 1
+    record = json.loads(lines[0])
+    assert record["impl"] == "reference" and record["n_gpus"] == 2
+    assert record["config"]["rows_total"] == 2 * 5 * 817
