@@ -42,16 +42,18 @@ bool native_hidden(int64_t hidden) {
         || hidden == 768 || hidden == 1024;
 }
 
-// Branch element types: the reference's two (float16, float32) plus bfloat16.
-bool branch_dtype_supported(at::ScalarType type) {
+// Element types of `branch` (the reference's float16 / float32, plus bfloat16)
+// and of `normalized` / `grad_normalized` (float32 as in the reference, or one
+// of the two 16-bit types); both use the RLN_DTYPE_* codes.
+bool element_dtype_supported(at::ScalarType type) {
     return type == at::kHalf || type == at::kFloat || type == at::kBFloat16;
 }
 
-int32_t branch_dtype_code(at::ScalarType type) {
+int32_t element_dtype_code(at::ScalarType type) {
     if (type == at::kHalf) {
-        return RLN_BRANCH_FLOAT16;
+        return RLN_DTYPE_FLOAT16;
     }
-    return type == at::kBFloat16 ? RLN_BRANCH_BFLOAT16 : RLN_BRANCH_FLOAT32;
+    return type == at::kBFloat16 ? RLN_DTYPE_BFLOAT16 : RLN_DTYPE_FLOAT32;
 }
 
 at::ScalarType branch_dtype_from_code(int64_t code) {
@@ -108,7 +110,7 @@ void check_forward_inputs(
         "all tensors must be on the same HIP device");
     TORCH_CHECK(x.scalar_type() == at::kFloat, "x must use float32");
     TORCH_CHECK(
-        branch_dtype_supported(branch.scalar_type()), "branch must use float16 or float32");
+        element_dtype_supported(branch.scalar_type()), "branch must use float16 or float32");
     TORCH_CHECK(
         weight.scalar_type() == at::kFloat && bias.scalar_type() == at::kFloat,
         "weight and bias must use float32");
@@ -159,7 +161,7 @@ void check_backward_inputs(
     // reference's float32 case keeps its message.
     TORCH_CHECK(
         grad_updated.scalar_type() == at::kFloat
-            && branch_dtype_supported(grad_normalized.scalar_type())
+            && element_dtype_supported(grad_normalized.scalar_type())
             && updated.scalar_type() == at::kFloat && weight.scalar_type() == at::kFloat
             && mean.scalar_type() == at::kFloat && rstd.scalar_type() == at::kFloat,
         "all backward tensors must use float32");
@@ -251,7 +253,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> forward_l
     const auto stream = c10::cuda::getCurrentCUDAStream(x.device().index()).stream();
     uint32_t* mask_pointer =
         dropout ? reinterpret_cast<uint32_t*>(dropout_mask.data_ptr<int32_t>()) : nullptr;
-    const int32_t branch_dtype = branch_dtype_code(branch.scalar_type());
+    const int32_t branch_dtype = element_dtype_code(branch.scalar_type());
     int status = RLN_OK;
     if (device_seed != nullptr) {
         status = rln_sm100_forward_device_rng(
@@ -445,8 +447,8 @@ std::vector<at::Tensor> residual_layer_norm_backward_cuda(
         workspace_bytes,
         row_count,
         static_cast<int32_t>(hidden),
-        branch_dtype_code(branch_type),
-        branch_dtype_code(grad_normalized.scalar_type()),  // same RLN_DTYPE_* codes
+        element_dtype_code(branch_type),
+        element_dtype_code(grad_normalized.scalar_type()),
         dropout ? 1 : 0,
         static_cast<float>(dropout_p),
         deterministic ? 1 : 0,
@@ -486,7 +488,7 @@ class ResidualLayerNormFunction
         ctx->saved_data["dropout_p"] = dropout_p;
         ctx->saved_data["training"] = training;
         ctx->saved_data["branch_dtype"] =
-            static_cast<int64_t>(branch_dtype_code(branch.scalar_type()));
+            static_cast<int64_t>(element_dtype_code(branch.scalar_type()));
         ctx->saved_data["threads"] = threads;
         ctx->saved_data["block_rows"] = block_rows;
         ctx->saved_data["parameter_threads"] = parameter_threads;
