@@ -51,23 +51,27 @@ def time_cuda(function, warmup, iterations):
     }
 
 
-def make_cell(tokens, hidden, branch_dtype, dropout_p, implementation):
+def make_cell(tokens, hidden, branch_dtype, dropout_p, implementation, normalized_dtype=None):
     x = torch.randn(1, tokens, hidden, device="cuda", requires_grad=True)
     branch = torch.randn(1, tokens, hidden, device="cuda", dtype=branch_dtype, requires_grad=True)
     weight = torch.randn(hidden, device="cuda", requires_grad=True)
     bias = torch.randn(hidden, device="cuda", requires_grad=True)
     grad_updated = torch.randn(1, tokens, hidden, device="cuda")
-    grad_normalized = torch.randn(1, tokens, hidden, device="cuda")
+    grad_normalized = torch.randn(1, tokens, hidden, device="cuda").to(
+        normalized_dtype or torch.float32
+    )
 
     def forward():
         with torch.no_grad():
             return residual_layer_norm(
-                x, branch, weight, bias, dropout_p, 1e-5, True, implementation=implementation
+                x, branch, weight, bias, dropout_p, 1e-5, True, implementation=implementation,
+                normalized_dtype=normalized_dtype,
             )
 
     def training():
         outputs = residual_layer_norm(
-            x, branch, weight, bias, dropout_p, 1e-5, True, implementation=implementation
+            x, branch, weight, bias, dropout_p, 1e-5, True, implementation=implementation,
+            normalized_dtype=normalized_dtype,
         )
         return torch.autograd.grad(
             outputs, (x, branch, weight, bias), (grad_updated, grad_normalized)
@@ -81,7 +85,11 @@ def main():
     parser.add_argument("--hidden", type=int, nargs="+", default=[384])
     parser.add_argument("--tokens", type=int, nargs="+", default=[128, 256, 512, 1024, 2048, 4096])
     parser.add_argument("--dropout", type=float, default=0.15)
-    parser.add_argument("--branch-dtype", choices=("float16", "float32"), default="float16")
+    parser.add_argument("--branch-dtype", choices=("float16", "float32", "bfloat16"),
+                        default="float16")
+    parser.add_argument("--normalized-dtype", choices=("float32", "float16", "bfloat16"),
+                        default="float32",
+                        help="type of the `normalized` output (float32 = the reference's contract)")
     parser.add_argument("--warmup", type=int, default=100)
     parser.add_argument("--iterations", type=int, default=1000)
     arguments = parser.parse_args()
@@ -90,16 +98,19 @@ def main():
     if not status.available:
         raise SystemExit(f"native backend unavailable: {status.reason}")
     branch_dtype = getattr(torch, arguments.branch_dtype)
+    normalized_dtype = getattr(torch, arguments.normalized_dtype)
     for hidden in arguments.hidden:
         for tokens in arguments.tokens:
             record = {
                 "device": status.device, "tokens": tokens, "hidden": hidden,
-                "branch_dtype": arguments.branch_dtype, "dropout_p": arguments.dropout,
+                "branch_dtype": arguments.branch_dtype,
+                "normalized_dtype": arguments.normalized_dtype, "dropout_p": arguments.dropout,
                 "warmup": arguments.warmup, "iterations": arguments.iterations,
             }
             for implementation in ("gfx1010", "torch"):
                 forward, training = make_cell(
-                    tokens, hidden, branch_dtype, arguments.dropout, implementation
+                    tokens, hidden, branch_dtype, arguments.dropout, implementation,
+                    normalized_dtype,
                 )
                 record[f"{implementation}_forward"] = time_cuda(
                     forward, arguments.warmup, arguments.iterations
