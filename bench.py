@@ -5,18 +5,27 @@
 
 A step is one forward + one backward of the operator over one batch of
 synthetic rows (plus, on N > 1 GPUs, the NCCL all-reduce of the [2, H]
-grad_weight/grad_bias buffer).  The headline workload is H = 768 on 64 Mi fp32
-elements (87,381 rows, fp16 branch, dropout 0.1) per GPU; rows are sharded, so
-N GPUs process N x 87,381 rows of one global batch (weak scaling) and every
-rank passes its global row offset so that the dropout mask is the one of the
-unsharded call.
+grad_weight/grad_bias buffer), run through ``gfx1010_kernels.sharded`` -- the
+package's own row-sharded step, asynchronous all-reduce included.  The headline
+workload is H = 768 on 64 Mi fp32 elements (87,381 rows, fp16 branch, dropout
+0.1) per GPU; rows are sharded, so N GPUs process N x 87,381 rows of one global
+batch (weak scaling) and every rank passes its global row offset so that the
+dropout mask is the one of the unsharded call.
 
-Rank 0 prints ONE JSON line.  ``value`` is rows/s with inputs resident in HBM;
-``e2e`` is the same metric with inputs in pinned host memory and results copied
-back to the host inside the timed region; ``roofline`` describes the dominant
-kernel (the backward) against the measured HBM peak; ``cpu_baseline`` is the
-torch decomposition (the reference's CPU path) timed on this machine's cores.
-``--impl reference`` times only that CPU path.
+Rank 0 prints ONE JSON line.  ``value`` is rows/s with inputs resident in HBM:
+the K-step region is timed R times back to back (``regions``) and the median
+region is reported, with ``value_min`` / ``value_max``.  ``e2e`` is the same
+metric with inputs in pinned host memory and results copied back to the host
+inside the timed region; ``roofline`` describes the dominant kernel (the
+backward) against the measured HBM peak; ``cpu_baseline`` is the reference's
+CPU path (its torch decomposition) timed on this machine's cores.
+``strong_c5`` is the second scaling experiment: the fixed [64, 4096, 1024]
+batch split by rows over the N GPUs (strong scaling), with the same batch on
+one GPU timed in the same run as its baseline.  ``sharded_check`` (N > 1)
+verifies, outside the timed regions, the all-reduced gradients against the
+fp64 sum of the ranks' unreduced buffers and the ranks' dropout masks against
+an unsharded call; a false check makes the run fail.
+``--impl reference`` times only the CPU path.
 """
 
 from __future__ import annotations
@@ -200,12 +209,21 @@ class ClockSampler:
         if self._thread is not None:
             self._thread.join(timeout=5)
 
-    def summary(self, begin, end):
-        window = [(mhz, bits) for (stamp, mhz, bits) in self.samples if begin <= stamp <= end]
-        if not window:
+    def summary(self, spans):
+        """Median clock and the union of throttle reasons over the first of
+        ``spans`` -- (label, begin, end) on the perf_counter clock, narrowest
+        first -- that holds at least two samples.  The label of the span that
+        was used is always reported as ``window``."""
+        for label, begin, end in spans:
+            window = [(mhz, bits) for (stamp, mhz, bits) in self.samples if begin <= stamp <= end]
+            if len(window) >= 2:
+                break
+        else:
+            label = "all samples of the run"
             window = [(mhz, bits) for (_, mhz, bits) in self.samples]
         if not window:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0,
+                    "window": "no samples"}
         bits = 0
         for _, sample_bits in window:
             bits |= sample_bits
@@ -215,15 +233,39 @@ class ClockSampler:
             "sm_max_mhz": self.max_mhz,
             "reasons": reasons,
             "samples": len(window),
+            "window": label,
         }
+
+
+REFERENCE_PACKAGE_DIR = REPO / "oracle" / "_ref"
+
+
+def reference_public_call():
+    """The reference project's own ``residual_layer_norm`` (installed by
+    ``oracle/build_ref.py`` into ``oracle/_ref``), or None when it is absent.
+    Only for a process that has not imported this repository's package of the
+    same name: the reference arm runs in a process of its own."""
+    if not (REFERENCE_PACKAGE_DIR / "gfx1010_kernels" / "normalization.py").exists():
+        return None
+    if "gfx1010_kernels" in sys.modules:
+        raise RuntimeError("the reference package must be imported in a fresh process")
+    sys.path.insert(0, str(REFERENCE_PACKAGE_DIR))
+    try:
+        import gfx1010_kernels as reference_package
+    finally:
+        sys.path.remove(str(REFERENCE_PACKAGE_DIR))
+    if not Path(reference_package.__file__).resolve().is_relative_to(REFERENCE_PACKAGE_DIR):
+        raise RuntimeError("imported the wrong gfx1010_kernels package")
+    return reference_package.residual_layer_norm
 
 
 def time_cpu_reference(rows, hidden, branch_dtype, dropout_p, steps, warmup,
                        normalized_dtype=torch.float32):
-    """The reference's CPU path: its torch decomposition (F.dropout -> add ->
-    F.layer_norm) forward plus torch.autograd.grad, on all host threads."""
-    from oracle import rln_oracle
-
+    """The reference's CPU path on all host threads: forward through its public
+    call with ``implementation="torch"`` (F.dropout -> add -> F.layer_norm) plus
+    ``torch.autograd.grad``.  Returns (times, threads, kind): kind "reference"
+    when the reference's own package ran, "port" when only the restatement in
+    ``oracle/rln_oracle.py`` was available."""
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     x, branch, weight, bias, grad_updated, grad_normalized = draw_inputs(
@@ -231,17 +273,44 @@ def time_cpu_reference(rows, hidden, branch_dtype, dropout_p, steps, warmup,
     )
     leaves = [t.requires_grad_(True) for t in (x, branch, weight, bias)]
     grad_normalized = grad_normalized.to(normalized_dtype)
+    reference_call = reference_public_call()
+    if reference_call is not None:
+        kind = "reference"
+
+        def forward():
+            updated, normalized = reference_call(
+                *leaves, dropout_p, EPS, True, implementation="torch"
+            )
+            # a 16-bit `normalized` is one cast after the reference's float32 result
+            return updated, normalized.to(normalized_dtype)
+    else:
+        from oracle import rln_oracle
+
+        kind = "port"
+
+        def forward():
+            return rln_oracle.torch_decomposition(
+                *leaves, dropout_p, EPS, True, None, normalized_dtype
+            )
     times = []
     for index in range(warmup + steps):
         begin = time.perf_counter()
-        outputs = rln_oracle.torch_decomposition(
-            *leaves, dropout_p, EPS, True, None, normalized_dtype
-        )
+        outputs = forward()
         torch.autograd.grad(outputs, leaves, (grad_updated, grad_normalized))
         elapsed = time.perf_counter() - begin
         if index >= warmup:
             times.append(elapsed)
-    return times, threads
+    return times, threads, kind
+
+
+def cpu_sample_description(rows, rows_full, hidden, branch_dtype, dropout_p, kind):
+    what = ("the reference package's residual_layer_norm(implementation='torch')"
+            if kind == "reference" else "the restated torch decomposition")
+    return (
+        f"first {rows} rows of the {rows_full}-row workload per step "
+        f"(x fp32 [{rows},{hidden}], branch {str(branch_dtype).split('.')[-1]}, p={dropout_p}); "
+        f"{what} + torch.autograd.grad"
+    )
 
 
 def run_reference_arm(args, rank):
@@ -249,19 +318,16 @@ def run_reference_arm(args, rank):
         return 0
     rows_full, hidden, branch_dtype, dropout_p, normalized_dtype = workload(args.workload)
     rows = min(rows_full, CPU_SAMPLE_ROWS)
-    times, threads = time_cpu_reference(
+    times, threads, kind = time_cpu_reference(
         rows, hidden, branch_dtype, dropout_p, args.steps, args.warmup, normalized_dtype
     )
     total = sum(times)
     value = rows * len(times) / total
-    sample = (
-        f"first {rows} rows of the {rows_full}-row workload per step "
-        f"(x fp32 [{rows},{hidden}], branch {str(branch_dtype).split('.')[-1]}, p={dropout_p})"
-    )
     line = {
         "impl": "reference",
         "metric": METRIC,
         "value": value,
+        "value_median": rows / statistics.median(times),
         "unit": UNIT,
         "n_gpus": args.gpus,
         "steps": args.steps,
@@ -274,13 +340,35 @@ def run_reference_arm(args, rank):
         "data": "synthetic",
         "config": workload_config(args.workload, args.gpus),
         "cpu_baseline": {
-            "value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+            "value": value, "unit": UNIT, "cores": threads, "kind": kind,
+            "sample": cpu_sample_description(rows, rows_full, hidden, branch_dtype, dropout_p, kind),
         },
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
     return 0
+
+
+def cpu_baseline_record(workload_name):
+    """The ``cpu_baseline`` object of the native arm's line: the reference arm run
+    as a child process (so that the reference's package, which has this
+    package's name, gets an interpreter of its own) on 5 steps after 1 warm-up."""
+    completed = subprocess.run(
+        [sys.executable, str(Path(__file__).resolve()), "--impl", "reference",
+         "--workload", workload_name, "--steps", "5", "--warmup", "1"],
+        capture_output=True, text=True, timeout=900,
+        env={key: value for key, value in os.environ.items()
+             if key not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")},
+    )
+    lines = [line for line in completed.stdout.splitlines() if line.startswith("{")]
+    if completed.returncode != 0 or not lines:
+        raise RuntimeError(f"the CPU baseline run failed:\n{completed.stdout}{completed.stderr}")
+    record = json.loads(lines[-1])
+    baseline = record["cpu_baseline"]
+    baseline["value"] = record["value_median"]
+    baseline["sample"] += "; median of 5 steps"
+    return baseline
 
 
 def workload_config(name, gpus):
@@ -307,307 +395,350 @@ def workload_config(name, gpus):
     }
 
 
-def run_native_arm(args, rank, local_rank, world):
-    import torch.distributed as dist
+REGIONS = 11          # back-to-back timed regions of K steps; the median is reported
+C5 = "c5_64x4096x1024"
 
-    from gfx1010_kernels import _C, residual_layer_norm, residual_layer_norm_status
 
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py --impl native needs a CUDA device (no CPU fallback)")
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    status = residual_layer_norm_status(device)
-    if not status.available:
-        raise RuntimeError(f"native backend unavailable: {status.reason}")
-    if world > 1:
-        # a short timeout: a rank that stops calling collectives must surface as an
-        # error within minutes, not hold the GPUs for the default ten
-        # NCCL on a high-priority stream: the all-reduce of step i is launched
-        # while the forward of step i+1 already fills every SM with short CTAs;
-        # at equal priority its CTAs are placed only after the forward's grid has
-        # been handed out, i.e. at the forward's tail, and part of its latency
-        # shows.  With priority it takes the first slots that free up.
-        options = None
-        if not args.default_priority_collectives:
-            options = dist.ProcessGroupNCCL.Options()
-            options.is_high_priority_stream = True
-        dist.init_process_group(
-            "nccl", device_id=device, timeout=datetime.timedelta(seconds=120),
-            pg_options=options,
-        )
+class ShardRunner:
+    """This rank's rows of one workload, resident on the device, and the step on
+    them: ``gfx1010_kernels.sharded.sharded_forward_backward`` with
+    ``async_op=True``, every step handed the previous step's handle (the
+    all-reduce overlaps the next forward and is waited for before the next
+    backward).  With one rank there is no collective and the handle is inert."""
 
-    rows, hidden, branch_dtype, dropout_p, normalized_dtype = workload(args.workload)
-    branch_bytes = 4 if branch_dtype == torch.float32 else 2
-    normalized_bytes = 4 if normalized_dtype == torch.float32 else 2
-    skip_e2e = args.kernel_only
-    host = draw_inputs(rows, hidden, branch_dtype, seed=rank)
-    x, branch, weight, bias, grad_updated, grad_normalized = (t.to(device) for t in host)
-    grad_normalized = grad_normalized.to(normalized_dtype)
-    if world > 1:
-        # replicated parameters: every rank uses rank 0's values
-        dist.broadcast(weight, 0)
-        dist.broadcast(bias, 0)
-    row_base = rank * rows
-    seed = 0
-    flush = None
-    if rows * hidden * 4 <= 126e6:
-        flush = torch.zeros(256 << 20, dtype=torch.uint8, device=device)
+    def __init__(self, name, rows, row_base, rank_seed, device, world):
+        from gfx1010_kernels import sharded
 
-    def flush_l2():
+        self.sharded = sharded
+        _, self.hidden, self.branch_dtype, self.dropout_p, self.normalized_dtype = workload(name)
+        self.rows = rows
+        self.row_base = row_base
+        self.world = world
+        self.device = device
+        host = draw_inputs(rows, self.hidden, self.branch_dtype, seed=rank_seed)
+        (self.x, self.branch, self.weight, self.bias, self.grad_updated,
+         grad_normalized) = (t.to(device) for t in host)
+        self.grad_normalized = grad_normalized.to(self.normalized_dtype)
+        self.host = host
+        if world > 1:
+            import torch.distributed as dist
+
+            # replicated parameters: every rank uses rank 0's values
+            dist.broadcast(self.weight, 0)
+            dist.broadcast(self.bias, 0)
+        self.pending = None
+        self.flush = None
+        if rows * self.hidden * 4 <= 126e6:
+            self.flush = torch.zeros(256 << 20, dtype=torch.uint8, device=device)
+
+    def flush_l2(self):
         # Write a buffer twice the size of L2, then read it: the write evicts the
         # workload's lines, the read pushes the write's dirty lines out to HBM, so
         # that the kernel that runs next is not billed for their write-back.
-        flush.zero_()
-        flush.sum()
+        self.flush.zero_()
+        self.flush.sum()
 
+    def step(self, index, after_forward=None):
+        self.pending = self.sharded.sharded_forward_backward(
+            self.x, self.branch, self.weight, self.bias, self.grad_updated, self.grad_normalized,
+            row_base=self.row_base, dropout_p=self.dropout_p, eps=EPS, training=True,
+            seed=0, offset=4 * index, async_op=True, previous=self.pending,
+            after_forward=after_forward, all_reduce=self.world > 1,
+        )
+        return self.pending
 
-    forward_events, backward_events = [], []
-    pending = []
+    def finish(self):
+        if self.pending is not None:
+            self.pending.wait()
+            self.pending = None
 
-    def finish_pending():
-        while pending:
-            work, _buffer = pending.pop()
-            work.wait()
+    def fence(self):
+        self.finish()
+        torch.cuda.synchronize()
+        if self.world > 1:
+            import torch.distributed as dist
 
-    def step(index, record):
-        if record:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def warm(self, count, first):
+        for index in range(count):
+            if self.flush is not None:
+                self.flush_l2()
+            self.step(first + index)
+            if index % 50 == 49:
+                torch.cuda.synchronize()
+        self.finish()
+        torch.cuda.synchronize()
+
+    def timed_regions(self, regions, steps, first, run_step=None):
+        """``regions`` regions of ``steps`` steps, each bracketed by a fence
+        (pending collective, device, barrier) on both sides and timed with CUDA
+        events on the launching stream.  Returns the per-region milliseconds of
+        this rank and the index after the last step.  Workloads that fit in L2
+        are flushed before every step and timed step by step."""
+        run_step = run_step or (lambda index: self.step(index))
+        elapsed = []
+        index = first
+        for _ in range(regions):
+            self.fence()
+            start = torch.cuda.Event(enable_timing=True)
+            stop = torch.cuda.Event(enable_timing=True)
+            brackets = []
+            start.record()
+            for _ in range(steps):
+                if self.flush is not None:
+                    # the L2 flush is not part of a step: bracket every step on its own
+                    self.flush_l2()
+                    begin_event = torch.cuda.Event(enable_timing=True)
+                    end_event = torch.cuda.Event(enable_timing=True)
+                    begin_event.record()
+                run_step(index)
+                index += 1
+                if self.flush is not None:
+                    end_event.record()
+                    brackets.append((begin_event, end_event))
+            self.finish()
+            stop.record()
+            self.fence()
+            if brackets:
+                elapsed.append(sum(a.elapsed_time(b) for a, b in brackets))
+            else:
+                elapsed.append(start.elapsed_time(stop))
+        return elapsed, index
+
+    def kernel_pass(self, steps, first):
+        """The same steps with CUDA events around the two halves: mean
+        milliseconds of (forward + wait for the previous all-reduce) and of
+        (zeroing kernel + backward).  Run outside the timed regions: an event
+        between two kernels keeps the second from being scheduled while the
+        first drains, which slows the step."""
+        forward_events, backward_events = [], []
+        for index in range(steps):
+            if self.flush is not None:
+                self.flush_l2()
             e0 = torch.cuda.Event(enable_timing=True)
             e1 = torch.cuda.Event(enable_timing=True)
             e2 = torch.cuda.Event(enable_timing=True)
             e0.record()
-        updated, normalized, mean, rstd, mask = _C.residual_layer_norm_forward_seeded(
-            x, branch, weight, bias, dropout_p, EPS, True, 128, seed, 4 * index, row_base,
-            NORMALIZED_CODES[normalized_dtype],
-        )
-        # The backward is a persistent grid that fills every SM exactly once; a
-        # communication kernel still resident from the previous step would push
-        # part of it into a second wave.  So the previous all-reduce may overlap
-        # the forward (dynamically scheduled CTAs) but must be done before this.
-        finish_pending()
-        if record:
-            e1.record()
-        gradients = _C.residual_layer_norm_backward(
-            grad_updated, grad_normalized, updated, weight, mean, rstd, mask,
-            dropout_p, True, BRANCH_CODES[branch_dtype], 128, 64, 256, 1, True,
-        )
-        if record:
+            self.step(first + index, after_forward=e1.record)
             e2.record()
             forward_events.append((e0, e1))
             backward_events.append((e1, e2))
-        if world > 1:
-            # grad_weight and grad_bias are views of one [2, H] buffer.  The all-reduce
-            # is asynchronous: it runs on NCCL's stream under the NEXT step's forward
-            # (which does not depend on it) and is waited for before that step's
-            # backward is launched, and once more before the timed region ends.
-            buffer = gradients[2]._base if gradients[2]._base is not None else gradients[2]
-            pending.append((dist.all_reduce(buffer, async_op=True), buffer))
-        return normalized, gradients
-
-    def fence():
-        finish_pending()
+        self.finish()
         torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+        forward_ms = statistics.mean(a.elapsed_time(b) for a, b in forward_events)
+        backward_ms = statistics.mean(a.elapsed_time(b) for a, b in backward_events)
+        return forward_ms, backward_ms
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
 
-    # warm-up: W steps, then as many more as bring the loaded span to about a second
-    # (clock settling + clock samples).  The count is agreed between the ranks --
-    # every step contains a collective, so all ranks must run the same number.
-    def warm(count, first):
-        for index in range(count):
-            if flush is not None:
-                flush_l2()
-            step(first + index, False)
-            if index % 50 == 49:
-                torch.cuda.synchronize()
+def max_over_ranks(values, device, world):
+    """Element-wise maximum of a list of floats over the ranks."""
+    if world == 1:
+        return list(values)
+    import torch.distributed as dist
+
+    tensor = torch.tensor(list(values), device=device, dtype=torch.float64)
+    dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
+    return tensor.tolist()
+
+
+def sharded_check(runner, rank, world, rows_total, offset):
+    """Correctness of the multi-rank step, outside every timed region.
+
+    1. Every rank runs forward + backward on its shard through the raw entries
+       (no collective); the unreduced [2, H] buffers are gathered and summed in
+       float64.  The product step (``sharded_forward_backward`` with the same
+       Philox state) must return that sum on every rank: <= 1e-4 relative, with
+       the absolute floor 1e-5 * sqrt(rows_total) for columns that cancel.
+    2. The product step's row-local outputs must be the raw calls' bits.
+    3. Rank 0 runs ONE unsharded forward over all rows_total rows (zeros as
+       data: the mask depends on the Philox state and the global element index
+       only) and compares, bit for bit, the first and last 256 rows of every
+       rank's mask with the rows of the unsharded mask they correspond to.
+    """
+    import torch.distributed as dist
+
+    sharded = runner.sharded
+    device = runner.device
+    hidden = runner.hidden
+    updated, normalized, mean, rstd, mask = sharded._native_forward(
+        runner.x, runner.branch, runner.weight, runner.bias, runner.normalized_dtype,
+        runner.dropout_p, EPS, True, 0, offset, runner.row_base,
+    )
+    grad_x, grad_branch, parameters = sharded._native_backward(
+        runner.grad_updated, runner.grad_normalized, updated, runner.weight, mean, rstd, mask,
+        runner.dropout_p, True, runner.branch_dtype,
+    )
+    gathered = [torch.empty_like(parameters) for _ in range(world)]
+    dist.all_gather(gathered, parameters.contiguous())
+    expected = torch.stack(gathered).double().sum(0)
+    result = sharded.sharded_forward_backward(
+        runner.x, runner.branch, runner.weight, runner.bias, runner.grad_updated,
+        runner.grad_normalized, row_base=runner.row_base, dropout_p=runner.dropout_p, eps=EPS,
+        training=True, seed=0, offset=offset,
+    )
+    reduced = torch.stack((result.grad_weight, result.grad_bias)).double()
+    floor = 1e-5 * float(rows_total) ** 0.5
+    excess = (reduced - expected).abs() - (1e-4 * expected.abs() + floor)
+    gradients_ok = bool((excess <= 0).all().item())
+    worst_relative = float(
+        ((reduced - expected).abs() / expected.abs().clamp_min(floor)).max().item())
+    row_local_ok = all(
+        torch.equal(a, b) for a, b in (
+            (result.updated, updated), (result.normalized, normalized), (result.grad_x, grad_x),
+            (result.grad_branch, grad_branch), (result.mask, mask))
+    )
+    # masks: two windows per rank against one unsharded forward on rank 0
+    words_per_row = hidden // 32
+    window = min(256, runner.rows)
+    sample = torch.cat((mask[: window * words_per_row],
+                        mask[(runner.rows - window) * words_per_row:])).contiguous()
+    layout = torch.tensor([runner.row_base, runner.rows, window], device=device,
+                          dtype=torch.int64)
+    layouts = [torch.empty_like(layout) for _ in range(world)]
+    dist.all_gather(layouts, layout)
+    windows = [int(entry[2].item()) for entry in layouts]
+    masks_ok = True
+    if len(set(windows)) == 1:
+        samples = [torch.empty_like(sample) for _ in range(world)]
+        dist.all_gather(samples, sample)
+        if rank == 0:
+            zeros = torch.zeros(rows_total, hidden, device=device)
+            whole = sharded._native_forward(
+                zeros, zeros.to(runner.branch_dtype), runner.weight, runner.bias,
+                torch.float32, runner.dropout_p, EPS, True, 0, offset, 0,
+            )[4]
+            for entry, got in zip(layouts, samples):
+                base, count, width = (int(v) for v in entry.tolist())
+                want = torch.cat((
+                    whole[base * words_per_row: (base + width) * words_per_row],
+                    whole[(base + count - width) * words_per_row: (base + count) * words_per_row],
+                ))
+                masks_ok = masks_ok and torch.equal(got, want)
+            del zeros, whole
+    else:
+        masks_ok = False
+    flags = torch.tensor([gradients_ok, row_local_ok, masks_ok, worst_relative], device=device,
+                         dtype=torch.float64)
+    worst = flags.clone()
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    record = {
+        "ok": bool(flags[0] > 0 and flags[1] > 0 and flags[2] > 0),
+        "all_reduced_equals_fp64_sum_of_rank_buffers": bool(flags[0] > 0),
+        "worst_relative_error": float(worst[3]),
+        "tolerance": "1e-4 relative + 1e-5*sqrt(rows_total) absolute",
+        "row_local_outputs_bit_identical_to_raw_calls": bool(flags[1] > 0),
+        "rank_masks_equal_unsharded_mask": bool(flags[2] > 0),
+        "mask_rows_compared_per_rank": 2 * window,
+        "ranks": world,
+    }
+    torch.cuda.synchronize()
+    return record
+
+
+def run_strong_c5(args, rank, world, device):
+    """The fixed [64, 4096, 1024] batch (262,144 rows, fp16 branch, p = 0.1) split
+    by rows over the ranks: strong scaling.  With more than one rank the same
+    batch is then timed on rank 0 alone (the other ranks wait at a barrier), so
+    that the speed-up is taken inside one run on one box."""
+    from gfx1010_kernels.sharded import shard_bounds
+
+    rows_total, hidden, branch_dtype, dropout_p, normalized_dtype = workload(C5)
+    begin, end = shard_bounds(rows_total, world, rank)
+    steps = max(3, min(args.steps, 100))
+    regions = REGIONS if not args.kernel_only else 3
+    branch_bytes = 4 if branch_dtype == torch.float32 else 2
+    bytes_per_row = (forward_bytes_per_row(hidden, branch_bytes, True)
+                     + backward_bytes_per_row(hidden, branch_bytes, True))
+
+    def measure(runner, ranks):
+        runner.warm(max(args.warmup, 3) + 10, 0)
+        elapsed, index = runner.timed_regions(regions, steps, 1000)
+        elapsed = max_over_ranks(elapsed, device, ranks)
+        forward_ms, backward_ms = runner.kernel_pass(min(steps, 50), index)
+        forward_ms, backward_ms = max_over_ranks([forward_ms, backward_ms], device, ranks)
+        median = statistics.median(elapsed)
+        return {
+            "rows_s": rows_total * steps / (median * 1e-3),
+            "rows_s_min": rows_total * steps / (max(elapsed) * 1e-3),
+            "rows_s_max": rows_total * steps / (min(elapsed) * 1e-3),
+            "ms_per_step": median / steps,
+            "forward_plus_wait_ms": forward_ms,
+            "backward_ms": backward_ms,
+            "hbm_gbs_per_gpu": rows_total / ranks * bytes_per_row * steps / (median * 1e-3) / 1e9,
+        }
+
+    runner = ShardRunner(C5, end - begin, begin, 100 + rank, device, world)
+    record = {
+        "workload": C5, "scaling": "strong", "rows_total": rows_total,
+        "rows_per_gpu": end - begin, "hidden": hidden, "steps": steps, "regions": regions,
+        "n_gpus": world,
+    }
+    record.update(measure(runner, world))
+    if world > 1:
+        record["sharded_check"] = sharded_check(runner, rank, world, rows_total, 4 * 50000)
+    del runner
+    torch.cuda.empty_cache()
+    if world > 1:
+        import torch.distributed as dist
+
+        if rank == 0:
+            alone = ShardRunner(C5, rows_total, 0, 100, device, 1)
+            record["one_gpu"] = measure(alone, 1)
+            record["speedup_vs_one_gpu"] = record["rows_s"] / record["one_gpu"]["rows_s"]
+            del alone
+            torch.cuda.empty_cache()
+        dist.barrier()
         torch.cuda.synchronize()
+    return record
 
-    warm_begin = time.perf_counter()
-    base = max(args.warmup, 3)
-    warm(base, 0)
-    warmup_actual = base
-    if not args.kernel_only:
-        probe_begin = time.perf_counter()
-        warm(10, base)          # timed probe (the first steps above carry one-time set-up)
-        warmup_actual += 10
-        per_step = (time.perf_counter() - probe_begin) / 10
-        extra = int(min(5000, 1.0 / max(per_step, 1e-6)))
-        if world > 1:
-            agreed = torch.tensor([extra], device=device, dtype=torch.int64)
-            dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
-            extra = int(agreed.item())
-        warm(extra, warmup_actual)
-        warmup_actual += extra
 
-    run_step = step
-    if args.cuda_graph:
-        if world > 1:
-            raise RuntimeError("--cuda-graph is a single-GPU mode")
-        # One step (forward, zeroing kernel, backward and the allocator's work)
-        # recorded once; every replay re-runs it with the recorded Philox offset.
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            graph_outputs = step(warmup_actual, False)
+def public_api_device_step_ms(runner, steps, first):
+    """Mean milliseconds of the step through the public call --
+    ``residual_layer_norm(implementation="gfx1010")`` + ``torch.autograd.grad`` --
+    on this rank's device-resident tensors (no collective), CUDA events."""
+    from gfx1010_kernels import residual_layer_norm
 
-        def run_step(index, record):
-            graph.replay()
-            return graph_outputs
+    leaves = [t.detach().clone().requires_grad_(True)
+              for t in (runner.x, runner.branch, runner.weight, runner.bias)]
+    generator = torch.cuda.default_generators[runner.device.index]
 
-        for _ in range(10):
-            run_step(0, False)
+    def one(index):
+        updated, normalized = residual_layer_norm(
+            *leaves, runner.dropout_p, EPS, True, implementation="gfx1010",
+            normalized_dtype=runner.normalized_dtype,
+        )
+        return torch.autograd.grad(
+            (updated, normalized), leaves, (runner.grad_updated, runner.grad_normalized))
 
-    fence()
-    timed_begin = time.perf_counter()
+    del generator, first
+    for index in range(10):
+        one(index)
+    torch.cuda.synchronize()
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
-    step_events = []
+    brackets = []
     start.record()
-    for index in range(args.steps):
-        if flush is not None:
-            # the L2 flush is not part of a step: bracket every step on its own
-            flush_l2()
-            begin_event = torch.cuda.Event(enable_timing=True)
-            end_event = torch.cuda.Event(enable_timing=True)
-            begin_event.record()
-        run_step(warmup_actual + index, args.kernel_events_in_loop)
-        if flush is not None:
-            end_event.record()
-            step_events.append((begin_event, end_event))
-    finish_pending()
+    for index in range(steps):
+        if runner.flush is not None:
+            runner.flush_l2()
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record()
+        one(index)
+        if runner.flush is not None:
+            b.record()
+            brackets.append((a, b))
     stop.record()
-    fence()
-    timed_end = time.perf_counter()
-    elapsed_ms = start.elapsed_time(stop)
-    if step_events:
-        elapsed_ms = sum(a.elapsed_time(b) for a, b in step_events)
-    if not args.kernel_events_in_loop:
-        # per-kernel durations: same steps, same buffers, right after the timed region
-        for index in range(min(args.steps, 100)):
-            if flush is not None:
-                flush_l2()
-            step(warmup_actual + args.steps + index, True)
-        finish_pending()
-        torch.cuda.synchronize()
-    forward_ms = statistics.mean(a.elapsed_time(b) for a, b in forward_events)
-    backward_ms = statistics.mean(a.elapsed_time(b) for a, b in backward_events)
-    clocks = sampler.summary(timed_begin, timed_end)
-    if clocks["samples"] < 2:
-        clocks = sampler.summary(warm_begin, timed_end)
-        clocks["window"] = "warm-up + timed region (timed region shorter than the sampling interval)"
+    torch.cuda.synchronize()
+    if brackets:
+        return sum(a.elapsed_time(b) for a, b in brackets) / steps
+    return start.elapsed_time(stop) / steps
 
-    # end-to-end: pinned host inputs -> device -> public API fwd+bwd -> results back to host
-    if skip_e2e:
-        e2e = {"ms": float("nan"), "public_ms": float("nan"), "steps": 0, "h2d": 0, "d2h": 0}
-    else:
-        e2e = run_end_to_end(
-            args, device, host, weight, bias, dropout_p, world, residual_layer_norm,
-            normalized_dtype,
-        )
-    sampler.stop()
 
-    if world > 1:
-        stats = torch.tensor(
-            [elapsed_ms, e2e["ms"], forward_ms, backward_ms, e2e.get("public_ms", 0.0)],
-            device=device, dtype=torch.float64,
-        )
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms, forward_ms, backward_ms, e2e_public_ms = stats.tolist()
-    else:
-        e2e_ms = e2e["ms"]
-        e2e_public_ms = e2e.get("public_ms", 0.0)
-
-    if rank == 0:
-        peak, peak_kind = measured_peak_gbs()
-        total_rows = rows * world
-        value = total_rows * args.steps / (elapsed_ms * 1e-3)
-        fwd_row = forward_bytes_per_row(hidden, branch_bytes, dropout_p > 0, normalized_bytes)
-        bwd_row = backward_bytes_per_row(hidden, branch_bytes, dropout_p > 0, normalized_bytes)
-        fwd_bytes = fwd_row * rows
-        bwd_bytes = bwd_row * rows
-        fwd_gbs = fwd_bytes / (forward_ms * 1e-3) / 1e9
-        bwd_gbs = bwd_bytes / (backward_ms * 1e-3) / 1e9
-        step_gbs = (fwd_bytes + bwd_bytes) * world * args.steps / (elapsed_ms * 1e-3) / 1e9
-        cpu = None
-        if world == 1 and not args.kernel_only:
-            sample_rows = min(rows, CPU_SAMPLE_ROWS)
-            times, threads = time_cpu_reference(
-                sample_rows, hidden, branch_dtype, dropout_p, 5, 1, normalized_dtype
-            )
-            cpu = {
-                "value": sample_rows / statistics.median(times),
-                "unit": UNIT,
-                "cores": threads,
-                "kind": "port",
-                "sample": f"first {sample_rows} rows of the workload, median of 5 fwd+bwd runs "
-                          "of the torch decomposition (F.dropout + add + F.layer_norm + autograd)",
-            }
-        line = {
-            "metric": METRIC,
-            "value": value,
-            "unit": UNIT,
-            "n_gpus": world,
-            "steps": args.steps,
-            "warmup": args.warmup,
-            "warmup_actual": warmup_actual,
-            "ms_per_step": elapsed_ms / args.steps,
-            "higher_is_better": True,
-            "scaling": "weak",
-            "vs_baseline": None,
-            "dtype": "f32",
-            "data": "synthetic",
-            "config": workload_config(args.workload, world),
-            "launch": "one step recorded into a CUDA graph, replayed (fixed Philox offset)"
-            if args.cuda_graph else "eager (three launches per step through the extension)",
-            "hbm_gbs_step": step_gbs,
-            "hbm_frac_of_8000": step_gbs / (HBM_SPEC_GBS * world),
-            "hbm_frac_of_measured": step_gbs / (peak * world),
-            "kernels": {
-                "forward": {"ms": forward_ms, "gbs": fwd_gbs, "bytes_per_row": fwd_row},
-                "backward": {"ms": backward_ms, "gbs": bwd_gbs, "bytes_per_row": bwd_row},
-            },
-            "roofline": {
-                "kernel": "rln_backward_kernel",
-                "bound": "hbm",
-                "achieved": bwd_gbs,
-                "peak": peak,
-                "peak_kind": f"{peak_kind} copy bandwidth (burst)",
-                "unit": "GB/s",
-                "frac": bwd_gbs / peak,
-                "frac_of_8000": bwd_gbs / HBM_SPEC_GBS,
-                "traffic": NCU_BACKWARD_TRAFFIC_BYTES.get(args.workload),
-                "traffic_unit": "bytes per launch (ncu dram read + write)",
-                "algorithmic_bytes_per_launch": bwd_bytes,
-                "timing": "CUDA events around each backward launch, "
-                          + ("inside the timed steps" if args.kernel_events_in_loop
-                             else "in a pass of the same steps right after the timed region"),
-            },
-            "cpu_baseline": cpu,
-            "e2e": None if skip_e2e else {
-                "value": total_rows * e2e["steps"] / (e2e_ms * 1e-3),
-                "unit": UNIT,
-                "h2d_bytes_per_step": e2e["h2d"],
-                "d2h_bytes_per_step": e2e["d2h"],
-                "steps": e2e["steps"],
-                "path": "one C-ABI call per step on pinned host buffers "
-                        "(rln_sm100_host_forward_backward via gfx1010_kernels.host_pipeline): "
-                        "chunked copy-in / fwd+bwd kernels / copy-out on three streams; timed "
-                        "on the host clock around synchronous calls",
-                "public_api_value": total_rows * e2e["steps"] / (e2e_public_ms * 1e-3),
-                "public_api_path": "pinned host -> device copies, residual_layer_norm("
-                                   "implementation='gfx1010') + torch.autograd.grad, results "
-                                   "copied to pinned host, one stream",
-            },
-            "gpu_launches": 3 * args.steps,  # forward, zeroing kernel, backward
-            "clocks": clocks,
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    return 0
+@@NATIVE@@
 
 
 def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_layer_norm,

@@ -295,6 +295,128 @@ extern "C" int64_t rln_sm100_backward_workspace_bytes(
     return static_cast<int64_t>(grid) * 2 * hidden * static_cast<int64_t>(sizeof(float));
 }
 
+// Argument rules shared by every backward entry point.
+int rln::check_backward_call(const rln::BackwardCall& call, bool* vector_ok) {
+    if (!supported_hidden(call.hidden)) {
+        return RLN_ERR_HIDDEN_SIZE;
+    }
+    if (!supported_dtype(call.branch_dtype)) {
+        return RLN_ERR_BRANCH_DTYPE;
+    }
+    if (!supported_dtype(call.normalized_dtype)) {
+        return RLN_ERR_NORMALIZED_DTYPE;
+    }
+    if (call.rows <= 0) {
+        return RLN_ERR_ROW_COUNT;
+    }
+    if (!(call.dropout_p >= 0.0f && call.dropout_p < 1.0f)) {
+        return RLN_ERR_DROPOUT_P;
+    }
+    const bool dropout = call.dropout_active != 0;
+    if (call.grad_updated == nullptr || call.grad_normalized == nullptr
+        || call.updated == nullptr || call.weight == nullptr || call.mean == nullptr
+        || call.rstd == nullptr || call.grad_x == nullptr || call.grad_branch == nullptr
+        || (dropout && call.dropout_mask == nullptr)
+        || (call.parameters_required && call.grad_parameters == nullptr)) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    const uintptr_t branch_element = element_bytes(call.branch_dtype);
+    const uintptr_t normalized_element = element_bytes(call.normalized_dtype);
+    if (!aligned_to(call.grad_updated, 4)
+        || !aligned_to(call.grad_normalized, normalized_element)
+        || !aligned_to(call.updated, 4) || !aligned_to(call.weight, 4)
+        || !aligned_to(call.mean, 4) || !aligned_to(call.rstd, 4)
+        || !aligned_to(call.grad_x, 4) || !aligned_to(call.grad_branch, branch_element)
+        || (dropout && !aligned_to(call.dropout_mask, 4))
+        || (call.grad_parameters != nullptr && !aligned_to(call.grad_parameters, 4))) {
+        return RLN_ERR_ALIGNMENT;
+    }
+    *vector_ok = aligned_to(call.grad_updated, 16)
+        && aligned_to(call.grad_normalized, normalized_element * 4)
+        && aligned_to(call.updated, 16) && aligned_to(call.weight, 16)
+        && aligned_to(call.grad_x, 16) && aligned_to(call.grad_branch, branch_element * 4)
+        && (call.grad_parameters == nullptr || aligned_to(call.grad_parameters, 16));
+    if (call.normalized_dtype != RLN_DTYPE_FLOAT32 && !*vector_ok) {
+        // the narrow-gradient kernels exist in the vectorised form only
+        return RLN_ERR_ALIGNMENT;
+    }
+    return RLN_OK;
+}
+
+// Launches of one checked backward call.  `scratch` holds the per-CTA partials
+// (deterministic != 0; too small -> `scratch_error`).
+int rln::launch_backward_call(
+    const rln::BackwardCall& call,
+    bool vector_ok,
+    int sm_count,
+    bool deterministic,
+    void* scratch,
+    int64_t scratch_bytes,
+    int scratch_error,
+    cudaStream_t stream) {
+    const bool parameters = call.grad_parameters != nullptr;
+    const int grid = rln::backward_grid(call.hidden, call.rows, sm_count);
+    const bool two_pass = parameters && deterministic;
+    if (two_pass) {
+        const int64_t needed = static_cast<int64_t>(grid) * 2 * call.hidden
+            * static_cast<int64_t>(sizeof(float));
+        if (scratch == nullptr || scratch_bytes < needed || !aligned_to(scratch, 16)) {
+            return scratch_error;
+        }
+    }
+    rln::BackwardParams params;
+    params.grad_updated = call.grad_updated;
+    params.grad_normalized = call.grad_normalized;
+    params.updated = call.updated;
+    params.weight = call.weight;
+    params.mean = call.mean;
+    params.rstd = call.rstd;
+    params.mask = call.dropout_mask;
+    params.grad_x = call.grad_x;
+    params.grad_branch = call.grad_branch;
+    params.grad_parameters = call.grad_parameters;
+    params.partials = two_pass ? static_cast<float*>(scratch) : nullptr;
+    params.rows = call.rows;
+    params.scale = dropout_scale(call.dropout_p, call.dropout_active != 0);
+    params.deterministic = two_pass ? 1 : 0;
+    params.row_counter = nullptr;
+    params.dynamic_begin = 0;
+
+    if (parameters && !two_pass) {
+        // the atomics accumulate into a zeroed buffer
+        const cudaError_t error = aligned_to(call.grad_parameters, 16)
+            ? rln::launch_zero(call.grad_parameters, 2 * call.hidden, stream)
+            : cudaMemsetAsync(
+                  call.grad_parameters, 0, static_cast<size_t>(2) * call.hidden * sizeof(float),
+                  stream);
+        if (error != cudaSuccess) {
+            return cuda_failed(error);
+        }
+    }
+    cudaError_t error = rln::launch_backward(
+        call.hidden,
+        call.branch_dtype,
+        call.normalized_dtype,
+        call.dropout_active != 0,
+        parameters,
+        vector_ok,
+        params,
+        grid,
+        stream);
+    if (error != cudaSuccess) {
+        return cuda_failed(error);
+    }
+    if (two_pass) {
+        error = rln::launch_reduce_partials(
+            static_cast<const float*>(scratch), call.grad_parameters, grid, 2 * call.hidden,
+            stream);
+        if (error != cudaSuccess) {
+            return cuda_failed(error);
+        }
+    }
+    return RLN_OK;
+}
+
 extern "C" int rln_sm100_backward(
     const float* grad_updated,
     const void* grad_normalized,
@@ -316,108 +438,35 @@ extern "C" int rln_sm100_backward(
     float dropout_p,
     int32_t deterministic,
     void* stream_pointer) {
-    if (!supported_hidden(hidden)) {
-        return RLN_ERR_HIDDEN_SIZE;
-    }
-    if (!supported_dtype(branch_dtype)) {
-        return RLN_ERR_BRANCH_DTYPE;
-    }
-    if (!supported_dtype(normalized_dtype)) {
-        return RLN_ERR_NORMALIZED_DTYPE;
-    }
-    if (rows <= 0) {
-        return RLN_ERR_ROW_COUNT;
-    }
-    if (!(dropout_p >= 0.0f && dropout_p < 1.0f)) {
-        return RLN_ERR_DROPOUT_P;
-    }
-    if (grad_updated == nullptr || grad_normalized == nullptr || updated == nullptr
-        || weight == nullptr || mean == nullptr || rstd == nullptr || grad_x == nullptr
-        || grad_branch == nullptr || (dropout_active && dropout_mask == nullptr)) {
-        return RLN_ERR_NULL_POINTER;
-    }
-    const uintptr_t branch_element = element_bytes(branch_dtype);
-    const uintptr_t normalized_element = element_bytes(normalized_dtype);
-    if (!aligned_to(grad_updated, 4) || !aligned_to(grad_normalized, normalized_element)
-        || !aligned_to(updated, 4)
-        || !aligned_to(weight, 4) || !aligned_to(mean, 4) || !aligned_to(rstd, 4)
-        || !aligned_to(grad_x, 4) || !aligned_to(grad_branch, branch_element)
-        || (dropout_active && !aligned_to(dropout_mask, 4))
-        || (grad_parameters != nullptr && !aligned_to(grad_parameters, 4))) {
-        return RLN_ERR_ALIGNMENT;
-    }
-    const bool parameters = grad_parameters != nullptr;
-    const bool vector_ok = aligned_to(grad_updated, 16)
-        && aligned_to(grad_normalized, normalized_element * 4) && aligned_to(updated, 16)
-        && aligned_to(weight, 16) && aligned_to(grad_x, 16)
-        && aligned_to(grad_branch, branch_element * 4)
-        && (!parameters || aligned_to(grad_parameters, 16));
-    if (normalized_dtype != RLN_DTYPE_FLOAT32 && !vector_ok) {
-        // the narrow-gradient kernels exist in the vectorised form only
-        return RLN_ERR_ALIGNMENT;
-    }
-
-    int sm_count = 0;
-    const int status = current_sm_count(&sm_count);
+    rln::BackwardCall call;
+    call.grad_updated = grad_updated;
+    call.grad_normalized = grad_normalized;
+    call.updated = updated;
+    call.weight = weight;
+    call.mean = mean;
+    call.rstd = rstd;
+    call.dropout_mask = dropout_mask;
+    call.grad_x = grad_x;
+    call.grad_branch = grad_branch;
+    call.grad_parameters = grad_parameters;
+    call.parameters_required = false;
+    call.rows = rows;
+    call.hidden = hidden;
+    call.branch_dtype = branch_dtype;
+    call.normalized_dtype = normalized_dtype;
+    call.dropout_active = dropout_active;
+    call.dropout_p = dropout_p;
+    bool vector_ok = false;
+    int status = rln::check_backward_call(call, &vector_ok);
     if (status != RLN_OK) {
         return status;
     }
-    const int grid = rln::backward_grid(hidden, rows, sm_count);
-    const bool two_pass = parameters && deterministic != 0;
-    if (two_pass) {
-        const int64_t needed =
-            static_cast<int64_t>(grid) * 2 * hidden * static_cast<int64_t>(sizeof(float));
-        if (workspace == nullptr || workspace_bytes < needed || !aligned_to(workspace, 16)) {
-            return RLN_ERR_WORKSPACE;
-        }
+    int sm_count = 0;
+    status = current_sm_count(&sm_count);
+    if (status != RLN_OK) {
+        return status;
     }
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_pointer);
-
-    rln::BackwardParams params;
-    params.grad_updated = grad_updated;
-    params.grad_normalized = grad_normalized;
-    params.updated = updated;
-    params.weight = weight;
-    params.mean = mean;
-    params.rstd = rstd;
-    params.mask = dropout_mask;
-    params.grad_x = grad_x;
-    params.grad_branch = grad_branch;
-    params.grad_parameters = grad_parameters;
-    params.partials = static_cast<float*>(workspace);
-    params.rows = rows;
-    params.scale = dropout_scale(dropout_p, dropout_active != 0);
-    params.deterministic = two_pass ? 1 : 0;
-
-    if (parameters && !two_pass) {
-        // the atomics accumulate into a zeroed buffer
-        const cudaError_t error = aligned_to(grad_parameters, 16)
-            ? rln::launch_zero(grad_parameters, 2 * hidden, stream)
-            : cudaMemsetAsync(
-                  grad_parameters, 0, static_cast<size_t>(2) * hidden * sizeof(float), stream);
-        if (error != cudaSuccess) {
-            return cuda_failed(error);
-        }
-    }
-    cudaError_t error = rln::launch_backward(
-        hidden,
-        branch_dtype,
-        normalized_dtype,
-        dropout_active != 0,
-        parameters,
-        vector_ok,
-        params,
-        grid,
-        stream);
-    if (error != cudaSuccess) {
-        return cuda_failed(error);
-    }
-    if (two_pass) {
-        error = rln::launch_reduce_partials(
-            static_cast<const float*>(workspace), grad_parameters, grid, 2 * hidden, stream);
-        if (error != cudaSuccess) {
-            return cuda_failed(error);
-        }
-    }
-    return RLN_OK;
+    return rln::launch_backward_call(
+        call, vector_ok, sm_count, deterministic != 0, workspace, workspace_bytes,
+        RLN_ERR_WORKSPACE, static_cast<cudaStream_t>(stream_pointer));
 }

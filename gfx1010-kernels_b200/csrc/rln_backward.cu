@@ -77,11 +77,12 @@ cudaError_t launch_zero(float* out, int count, cudaStream_t stream) {
     const int blocks = (count4 + kThreads - 1) / kThreads;
     return launch_dependent(
         rln_zero_kernel<kThreads>,
-        static_cast<unsigned>(blocks),
+        static_cast<unsigned>(blocks > 0 ? blocks : 1),
         kThreads,
         stream,
         reinterpret_cast<float4*>(out),
-        count4);
+        count4,
+        static_cast<uint4*>(nullptr));
 }
 
 }  // namespace rln

@@ -67,10 +67,6 @@ int scratch_on_current_device(void** address, int* sm_count) {
     return RLN_OK;
 }
 
-bool aligned_to(const void* pointer, uintptr_t bytes) {
-    return (reinterpret_cast<uintptr_t>(pointer) & (bytes - 1)) == 0;
-}
-
 }  // namespace
 
 extern "C" int rln_sm100_backward_static_scratch(
@@ -90,88 +86,42 @@ extern "C" int rln_sm100_backward_static_scratch(
     int32_t dropout_active,
     float dropout_p,
     void* stream_pointer) {
-    if (!(hidden == 128 || hidden == 256 || hidden == 384 || hidden == 512 || hidden == 768
-          || hidden == 1024)) {
-        return RLN_ERR_HIDDEN_SIZE;
-    }
-    if (branch_dtype != RLN_BRANCH_FLOAT32 && branch_dtype != RLN_BRANCH_FLOAT16
-        && branch_dtype != RLN_BRANCH_BFLOAT16) {
-        return RLN_ERR_BRANCH_DTYPE;
-    }
-    if (rows <= 0) {
-        return RLN_ERR_ROW_COUNT;
-    }
-    if (!(dropout_p >= 0.0f && dropout_p < 1.0f)) {
-        return RLN_ERR_DROPOUT_P;
-    }
-    if (grad_updated == nullptr || grad_normalized == nullptr || updated == nullptr
-        || weight == nullptr || mean == nullptr || rstd == nullptr || grad_x == nullptr
-        || grad_branch == nullptr || grad_parameters == nullptr
-        || (dropout_active && dropout_mask == nullptr)) {
-        return RLN_ERR_NULL_POINTER;
-    }
-    const uintptr_t branch_element = branch_dtype == RLN_BRANCH_FLOAT32 ? 4 : 2;
-    if (!aligned_to(grad_updated, 4) || !aligned_to(grad_normalized, 4) || !aligned_to(updated, 4)
-        || !aligned_to(weight, 4) || !aligned_to(mean, 4) || !aligned_to(rstd, 4)
-        || !aligned_to(grad_x, 4) || !aligned_to(grad_branch, branch_element)
-        || !aligned_to(grad_parameters, 4) || (dropout_active && !aligned_to(dropout_mask, 4))) {
-        return RLN_ERR_ALIGNMENT;
-    }
-    const bool vector_ok = aligned_to(grad_updated, 16) && aligned_to(grad_normalized, 16)
-        && aligned_to(updated, 16) && aligned_to(weight, 16) && aligned_to(grad_x, 16)
-        && aligned_to(grad_branch, branch_element * 4) && aligned_to(grad_parameters, 16);
-
-    void* scratch = nullptr;
-    int sm_count = 0;
-    const int status = scratch_on_current_device(&scratch, &sm_count);
+    rln::BackwardCall call;
+    call.grad_updated = grad_updated;
+    call.grad_normalized = grad_normalized;  // this entry takes float32 only
+    call.updated = updated;
+    call.weight = weight;
+    call.mean = mean;
+    call.rstd = rstd;
+    call.dropout_mask = dropout_mask;
+    call.grad_x = grad_x;
+    call.grad_branch = grad_branch;
+    call.grad_parameters = grad_parameters;
+    call.parameters_required = true;
+    call.rows = rows;
+    call.hidden = hidden;
+    call.branch_dtype = branch_dtype;
+    call.normalized_dtype = RLN_DTYPE_FLOAT32;
+    call.dropout_active = dropout_active;
+    call.dropout_p = dropout_p;
+    bool vector_ok = false;
+    int status = rln::check_backward_call(call, &vector_ok);
     if (status != RLN_OK) {
         return status;
     }
-    const int grid = rln::backward_grid(hidden, rows, sm_count);
-    const int64_t needed =
-        static_cast<int64_t>(grid) * 2 * hidden * static_cast<int64_t>(sizeof(float));
-    if (needed > static_cast<int64_t>(RLN_STATIC_SCRATCH_BYTES)) {
-        return RLN_ERR_LIMIT;
+    void* scratch = nullptr;
+    int sm_count = 0;
+    status = scratch_on_current_device(&scratch, &sm_count);
+    if (status != RLN_OK) {
+        return status;
     }
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_pointer);
-
-    rln::BackwardParams params;
-    params.grad_updated = grad_updated;
-    params.grad_normalized = grad_normalized;
-    params.updated = updated;
-    params.weight = weight;
-    params.mean = mean;
-    params.rstd = rstd;
-    params.mask = dropout_mask;
-    params.grad_x = grad_x;
-    params.grad_branch = grad_branch;
-    params.grad_parameters = grad_parameters;
-    params.partials = static_cast<float*>(scratch);
-    params.rows = rows;
-    params.scale = dropout_active ? 1.0f / (1.0f - dropout_p) : 1.0f;
-    params.deterministic = 1;
-
     // Nothing in the scratch has to start at zero: every CTA of the grid stores
     // its whole [2, hidden] partial before the reduction reads partials
     // 0 .. grid-1, and entries left over from an earlier, larger call lie
-    // beyond `grid` and are never read.
-    cudaError_t error = rln::launch_backward(
-        hidden,
-        branch_dtype,
-        RLN_DTYPE_FLOAT32,  // this entry takes a float32 grad_normalized only
-        dropout_active != 0,
-        /*parameters=*/true,
-        vector_ok,
-        params,
-        grid,
-        stream);
-    if (error != cudaSuccess) {
-        return rln::record_cuda_error(error);
-    }
-    error = rln::launch_reduce_partials(
-        static_cast<const float*>(scratch), grad_parameters, grid, 2 * hidden, stream);
-    if (error != cudaSuccess) {
-        return rln::record_cuda_error(error);
-    }
-    return RLN_OK;
+    // beyond `grid` and are never read.  A grid whose partials do not fit in
+    // the array gets RLN_ERR_LIMIT.
+    return rln::launch_backward_call(
+        call, vector_ok, sm_count, /*deterministic=*/true, scratch,
+        static_cast<int64_t>(RLN_STATIC_SCRATCH_BYTES), RLN_ERR_LIMIT,
+        static_cast<cudaStream_t>(stream_pointer));
 }

@@ -28,7 +28,7 @@ cudaError_t launch_forward_typed(const ForwardParams& params, int sm_count, cuda
     if constexpr (kLanes == kWarpSize) {
         return launch_dependent(
             rln_forward_kernel<H, BranchT, kDropout, kAligned, kWarps, kRows, kMinCtas,
-                               kDeviceRng, false, NormT>,
+                               kDeviceRng, false, NormT, ForwardTune<H>::kPacked>,
             static_cast<unsigned>(blocks),
             kWarps * kWarpSize,
             stream,
@@ -36,7 +36,7 @@ cudaError_t launch_forward_typed(const ForwardParams& params, int sm_count, cuda
     } else {
         return launch_dependent(
             rln_forward_subwarp_kernel<H, BranchT, kDropout, kAligned, kWarps, kLanes, kMinCtas,
-                                       kDeviceRng, false, NormT>,
+                                       kDeviceRng, false, NormT, ForwardTune<H>::kPacked>,
             static_cast<unsigned>(blocks),
             kWarps * kWarpSize,
             stream,

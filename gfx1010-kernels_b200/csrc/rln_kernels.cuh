@@ -85,6 +85,12 @@ struct BackwardParams {
     int64_t rows;
     float scale;
     int deterministic;
+    // Kernels instantiated with kDynamicRows (variant benchmark only): rows
+    // below dynamic_begin (a multiple of the grid's stride, at least one stride)
+    // are split statically, the rows from there on are claimed from
+    // row_counter, which is zeroed before the launch.
+    unsigned int* row_counter;
+    int64_t dynamic_begin;
 };
 
 // ---------------------------------------------------------------------------
@@ -104,10 +110,14 @@ __device__ __forceinline__ void grid_dependency_sync() {
 // the programmatic dependency between the forward and the backward).
 template <int kThreads>
 __global__ void __launch_bounds__(kThreads)
-rln_zero_kernel(float4* __restrict__ out, int count4) {
+rln_zero_kernel(float4* __restrict__ out, int count4, uint4* __restrict__ extra) {
     grid_dependency_sync();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < count4; i += gridDim.x * blockDim.x) {
         out[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    // the backward's row counter (one 16-byte word somewhere else), if any
+    if (extra != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        *extra = make_uint4(0u, 0u, 0u, 0u);
     }
 }
 
@@ -400,20 +410,140 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// ---------------------------------------------------------------------------
+// Two optional forms of the arithmetic core.  Both are template parameters of
+// the kernels (the variant benchmark times every combination; the launch tables
+// in rln_launch.h say what ships).
+//   kPacked     two-wide fp32 instructions (add/mul/fma .f32x2 of sm_100) on
+//               the (x, y) and (z, w) halves of a chunk.  Every lane-local
+//               operation keeps its rounding (round-to-nearest, no flush), so
+//               `updated` and the affine output are the bits of the scalar
+//               form; only the association of the per-lane partial sums
+//               differs.  Pays where the forward runs at 32 warps per SM on a
+//               64-register budget (H = 384: +6 %); neutral or slower elsewhere.
+//   RLN_FWD_MASK_REDUX (macro, 0)  the eight lanes of a mask word combine their
+//               nibbles with one redux.sync.or over the lane group instead of
+//               three shuffle + or steps.  Measured 25 % slower for the forward
+//               (a redux over a partial member mask is far from one shuffle's
+//               cost), so it stays off.
+// ---------------------------------------------------------------------------
+#ifndef RLN_FWD_MASK_REDUX
+#define RLN_FWD_MASK_REDUX 0
+#endif
+
+__device__ __forceinline__ float2 lo2(float4 v) { return make_float2(v.x, v.y); }
+__device__ __forceinline__ float2 hi2(float4 v) { return make_float2(v.z, v.w); }
+__device__ __forceinline__ float4 join4(float2 lo, float2 hi) {
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
+
+// OR of `word` over the aligned group of eight lanes this lane belongs to.
+__device__ __forceinline__ uint32_t or_over_eight_lanes(uint32_t word, int lane) {
+#if RLN_FWD_MASK_REDUX
+    return __reduce_or_sync(0xffu << (lane & 24), word);
+#else
+    word |= __shfl_xor_sync(kFullMask, word, 1);
+    word |= __shfl_xor_sync(kFullMask, word, 2);
+    word |= __shfl_xor_sync(kFullMask, word, 4);
+    return word;
+#endif
+}
+
+// keep ? scale : 0 for the four columns of a chunk, times v, one rounding each.
+template <bool kPacked>
+__device__ __forceinline__ float4 scale_kept(float4 v, uint32_t nibble, float scale) {
+    if constexpr (kPacked) {
+        return join4(
+            __fmul2_rn(lo2(v), make_float2((nibble & 1u) ? scale : 0.0f,
+                                           (nibble & 2u) ? scale : 0.0f)),
+            __fmul2_rn(hi2(v), make_float2((nibble & 4u) ? scale : 0.0f,
+                                           (nibble & 8u) ? scale : 0.0f)));
+    } else {
+        return make_float4(__fmul_rn(v.x, (nibble & 1u) ? scale : 0.0f),
+                           __fmul_rn(v.y, (nibble & 2u) ? scale : 0.0f),
+                           __fmul_rn(v.z, (nibble & 4u) ? scale : 0.0f),
+                           __fmul_rn(v.w, (nibble & 8u) ? scale : 0.0f));
+    }
+}
+
 // dropped = round_to_branch(float(b) * keep * scale) for the four columns of a
 // chunk; `nibble` holds their keep bits.  One multiply by (keep ? scale : 0)
 // gives the same bits as the two multiplies of the torch decomposition
 // evaluated with this mask -- b * 1 * scale == b * scale and
 // b * 0 * scale == b * 0 including the sign of zero, and a non-finite b times
 // zero is NaN either way -- and the sum is never contracted into an fma.
-template <typename BranchT>
+template <typename BranchT, bool kPacked>
 __device__ __forceinline__ float4 drop_four(float4 b, uint32_t nibble, float scale) {
-    float4 dropped;
-    dropped.x = __fmul_rn(b.x, (nibble & 1u) ? scale : 0.0f);
-    dropped.y = __fmul_rn(b.y, (nibble & 2u) ? scale : 0.0f);
-    dropped.z = __fmul_rn(b.z, (nibble & 4u) ? scale : 0.0f);
-    dropped.w = __fmul_rn(b.w, (nibble & 8u) ? scale : 0.0f);
-    return BranchIO<BranchT>::round4(dropped);
+    return BranchIO<BranchT>::round4(scale_kept<kPacked>(b, nibble, scale));
+}
+
+// Lane-local pieces of the row arithmetic, shared by the two forward kernels.
+// u = x + dropped, never contracted into an fma with the dropout multiply.
+template <bool kPacked>
+__device__ __forceinline__ float4 add_residual(float4 x, float4 dropped) {
+    if constexpr (kPacked) {
+        return join4(__fadd2_rn(lo2(x), lo2(dropped)), __fadd2_rn(hi2(x), hi2(dropped)));
+    } else {
+        return make_float4(__fadd_rn(x.x, dropped.x), __fadd_rn(x.y, dropped.y),
+                           __fadd_rn(x.z, dropped.z), __fadd_rn(x.w, dropped.w));
+    }
+}
+
+// A lane's running sum over its chunks (values, or squares of centred values).
+template <bool kPacked>
+struct LaneSum;
+
+template <>
+struct LaneSum<true> {
+    float2 acc = {0.0f, 0.0f};
+    __device__ __forceinline__ void add(float4 v) {
+        acc = __fadd2_rn(acc, __fadd2_rn(lo2(v), hi2(v)));
+    }
+    __device__ __forceinline__ void add_centred_square(float4 v, float mean) {
+        const float2 shift = splat2(-mean);
+        const float2 a = __fadd2_rn(lo2(v), shift);
+        const float2 b = __fadd2_rn(hi2(v), shift);
+        acc = __ffma2_rn(a, a, acc);
+        acc = __ffma2_rn(b, b, acc);
+    }
+    __device__ __forceinline__ float total() const { return acc.x + acc.y; }
+};
+
+template <>
+struct LaneSum<false> {
+    float acc = 0.0f;
+    __device__ __forceinline__ void add(float4 v) { acc += (v.x + v.y) + (v.z + v.w); }
+    __device__ __forceinline__ void add_centred_square(float4 v, float mean) {
+        const float cx = v.x - mean;
+        const float cy = v.y - mean;
+        const float cz = v.z - mean;
+        const float cw = v.w - mean;
+        acc += (cx * cx + cy * cy) + (cz * cz + cw * cw);
+    }
+    __device__ __forceinline__ float total() const { return acc; }
+};
+
+// (u - mean) * rstd * gamma + beta for the four columns of a chunk.
+template <bool kPacked>
+__device__ __forceinline__ float4 normalize_affine(
+    float4 u, float mean, float rstd, float4 gamma, float4 beta) {
+    if constexpr (kPacked) {
+        const float2 shift = splat2(-mean);
+        const float2 scale = splat2(rstd);
+        const float2 lo = __ffma2_rn(
+            __fmul2_rn(__fadd2_rn(lo2(u), shift), scale), lo2(gamma), lo2(beta));
+        const float2 hi = __ffma2_rn(
+            __fmul2_rn(__fadd2_rn(hi2(u), shift), scale), hi2(gamma), hi2(beta));
+        return join4(lo, hi);
+    } else {
+        float4 out;
+        out.x = (u.x - mean) * rstd * gamma.x + beta.x;
+        out.y = (u.y - mean) * rstd * gamma.y + beta.y;
+        out.z = (u.z - mean) * rstd * gamma.z + beta.z;
+        out.w = (u.w - mean) * rstd * gamma.w + beta.w;
+        return out;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -421,7 +551,7 @@ __device__ __forceinline__ float4 drop_four(float4 b, uint32_t nibble, float sca
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kRows,
           int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = false,
-          typename NormT = float>
+          typename NormT = float, bool kPacked = false>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_kernel(const ForwardParams p) {
     static_assert(H % 128 == 0, "hidden must be a multiple of 128");
@@ -499,34 +629,26 @@ rln_forward_kernel(const ForwardParams p) {
             if (row >= p.rows) {
                 continue;  // warp-uniform
             }
-            float sum = 0.0f;
+            LaneSum<kPacked> sum;
 #pragma unroll
             for (int k = 0; k < V; ++k) {
                 float4 dropped = b[r][k];
                 if constexpr (kDropout) {
-                    dropped = drop_four<BranchT>(dropped, nibble[r][k], p.scale);
+                    dropped = drop_four<BranchT, kPacked>(dropped, nibble[r][k], p.scale);
                 }
-                float4 value = u[r][k];
-                value.x = __fadd_rn(value.x, dropped.x);
-                value.y = __fadd_rn(value.y, dropped.y);
-                value.z = __fadd_rn(value.z, dropped.z);
-                value.w = __fadd_rn(value.w, dropped.w);
+                const float4 value = add_residual<kPacked>(u[r][k], dropped);
                 u[r][k] = value;
                 const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
                 store_f4<kAligned, kStreamHints>(p.updated, chunk, value);
-                sum += (value.x + value.y) + (value.z + value.w);
+                sum.add(value);
             }
-            const float row_mean = warp_sum(sum) * kInvH;
-            float square_sum = 0.0f;
+            const float row_mean = warp_sum(sum.total()) * kInvH;
+            LaneSum<kPacked> square_sum;
 #pragma unroll
             for (int k = 0; k < V; ++k) {
-                const float cx = u[r][k].x - row_mean;
-                const float cy = u[r][k].y - row_mean;
-                const float cz = u[r][k].z - row_mean;
-                const float cw = u[r][k].w - row_mean;
-                square_sum += (cx * cx + cy * cy) + (cz * cz + cw * cw);
+                square_sum.add_centred_square(u[r][k], row_mean);
             }
-            const float variance = warp_sum(square_sum) * kInvH;
+            const float variance = warp_sum(square_sum.total()) * kInvH;
             const float row_rstd = rsqrtf(variance + p.eps);
             if (lane == 0) {
                 p.mean[row] = row_mean;
@@ -537,11 +659,7 @@ rln_forward_kernel(const ForwardParams p) {
                 const int pchunk = lane + k * kWarpSize;
                 const float4 gamma = load_param<kAligned>(p.weight, pchunk);
                 const float4 beta = load_param<kAligned>(p.bias, pchunk);
-                float4 out;
-                out.x = (u[r][k].x - row_mean) * row_rstd * gamma.x + beta.x;
-                out.y = (u[r][k].y - row_mean) * row_rstd * gamma.y + beta.y;
-                out.z = (u[r][k].z - row_mean) * row_rstd * gamma.z + beta.z;
-                out.w = (u[r][k].w - row_mean) * row_rstd * gamma.w + beta.w;
+                const float4 out = normalize_affine<kPacked>(u[r][k], row_mean, row_rstd, gamma, beta);
                 // rounded once to NormT (identity for float32)
                 BranchIO<NormT>::template store<kAligned, kStreamHints>(
                     p.normalized, row * kChunksPerRow + pchunk, out);
@@ -551,10 +669,8 @@ rln_forward_kernel(const ForwardParams p) {
                 // (lane & 7) of mask word 4k + lane/8.
 #pragma unroll
                 for (int k = 0; k < V; ++k) {
-                    uint32_t word = nibble[r][k] << (4 * (lane & 7));
-                    word |= __shfl_xor_sync(kFullMask, word, 1);
-                    word |= __shfl_xor_sync(kFullMask, word, 2);
-                    word |= __shfl_xor_sync(kFullMask, word, 4);
+                    const uint32_t word =
+                        or_over_eight_lanes(nibble[r][k] << (4 * (lane & 7)), lane);
                     if ((lane & 7) == 0) {
                         p.mask[row * kWordsPerRow + 4 * k + (lane >> 3)] = word;
                     }
@@ -575,7 +691,7 @@ rln_forward_kernel(const ForwardParams p) {
 // ---------------------------------------------------------------------------
 template <int H, typename BranchT, bool kDropout, bool kAligned, int kWarps, int kLanes,
           int kMinCtas = 1, bool kDeviceRng = false, bool kStreamHints = false,
-          typename NormT = float>
+          typename NormT = float, bool kPacked = false>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_forward_subwarp_kernel(const ForwardParams p) {
     static_assert(kLanes == 8 || kLanes == 16, "a row is owned by 8 or 16 lanes");
@@ -642,39 +758,33 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             }
         }
 
-        float sum = 0.0f;
+        LaneSum<kPacked> lane_sum;
 #pragma unroll
         for (int k = 0; k < V; ++k) {
             float4 dropped = b[k];
             if constexpr (kDropout) {
-                dropped = drop_four<BranchT>(dropped, nibble[k], p.scale);
+                dropped = drop_four<BranchT, kPacked>(dropped, nibble[k], p.scale);
             }
-            float4 value = u[k];
-            value.x = __fadd_rn(value.x, dropped.x);
-            value.y = __fadd_rn(value.y, dropped.y);
-            value.z = __fadd_rn(value.z, dropped.z);
-            value.w = __fadd_rn(value.w, dropped.w);
+            const float4 value = add_residual<kPacked>(u[k], dropped);
             u[k] = value;
             if (valid) {
                 store_f4<kAligned, kStreamHints>(
                     p.updated, row * kChunksPerRow + lane_in_row + k * kLanes, value);
             }
-            sum += (value.x + value.y) + (value.z + value.w);
+            lane_sum.add(value);
         }
+        float sum = lane_sum.total();
 #pragma unroll
         for (int delta = kLanes / 2; delta > 0; delta >>= 1) {
             sum += __shfl_xor_sync(kFullMask, sum, delta);
         }
         const float row_mean = sum * kInvH;
-        float square_sum = 0.0f;
+        LaneSum<kPacked> lane_squares;
 #pragma unroll
         for (int k = 0; k < V; ++k) {
-            const float cx = u[k].x - row_mean;
-            const float cy = u[k].y - row_mean;
-            const float cz = u[k].z - row_mean;
-            const float cw = u[k].w - row_mean;
-            square_sum += (cx * cx + cy * cy) + (cz * cz + cw * cw);
+            lane_squares.add_centred_square(u[k], row_mean);
         }
+        float square_sum = lane_squares.total();
 #pragma unroll
         for (int delta = kLanes / 2; delta > 0; delta >>= 1) {
             square_sum += __shfl_xor_sync(kFullMask, square_sum, delta);
@@ -689,11 +799,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             const int pchunk = lane_in_row + k * kLanes;
             const float4 gamma = load_param<kAligned>(p.weight, pchunk);
             const float4 beta = load_param<kAligned>(p.bias, pchunk);
-            float4 out;
-            out.x = (u[k].x - row_mean) * row_rstd * gamma.x + beta.x;
-            out.y = (u[k].y - row_mean) * row_rstd * gamma.y + beta.y;
-            out.z = (u[k].z - row_mean) * row_rstd * gamma.z + beta.z;
-            out.w = (u[k].w - row_mean) * row_rstd * gamma.w + beta.w;
+            const float4 out = normalize_affine<kPacked>(u[k], row_mean, row_rstd, gamma, beta);
             if (valid) {
                 BranchIO<NormT>::template store<kAligned, kStreamHints>(
                     p.normalized, row * kChunksPerRow + pchunk, out);
@@ -703,10 +809,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             // chunk c = lane_in_row + kLanes*k -> nibble (c & 7) of word c / 8
 #pragma unroll
             for (int k = 0; k < V; ++k) {
-                uint32_t word = nibble[k] << (4 * (lane & 7));
-                word |= __shfl_xor_sync(kFullMask, word, 1);
-                word |= __shfl_xor_sync(kFullMask, word, 2);
-                word |= __shfl_xor_sync(kFullMask, word, 4);
+                const uint32_t word = or_over_eight_lanes(nibble[k] << (4 * (lane & 7)), lane);
                 if (valid && (lane & 7) == 0) {
                     p.mask[row * kWordsPerRow + (lane_in_row + k * kLanes) / 8] = word;
                 }
@@ -716,9 +819,22 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
 }
 
 // ---------------------------------------------------------------------------
-// Backward.  Persistent grid; each warp walks groups of kRows consecutive rows
-// with a fixed stride, so the set and order of rows a warp (and a CTA) sums is
-// a pure function of (rows, gridDim) -- the basis of the bitwise-replay mode.
+// Backward.  Persistent grid.  Two ways of handing rows to warps:
+//   static   (kDynamicRows == false) each warp walks groups of kRows
+//            consecutive rows with a fixed stride, so the set and order of
+//            rows a warp (and a CTA) sums is a pure function of (rows,
+//            gridDim) -- the basis of the bitwise-replay mode;
+//   dynamic  (kDynamicRows == true; instantiated by the variant benchmark only)
+//            rows below p.dynamic_begin are split statically as above, the
+//            groups from there on are claimed from a global counter, the claim
+//            issued right after the loads of the current group so that its
+//            latency hides behind them.  Measured on B200: claiming every row
+//            costs one atomic per row on a single address (1-2 ns each), which
+//            caps the grid below the row rate the static kernel reaches (8 %
+//            slower at H = 768, 50 % at H = 384); claiming only the last one to
+//            six rounds gains up to 4 % for the backward of 32,768 x 1,024 and
+//            87,381 x 768 and loses 1-7 % at H = 128, 384 and 512, so the
+//            library ships the static split only.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void red_add_f4(float* address, float4 v) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
@@ -727,8 +843,108 @@ __device__ __forceinline__ void red_add_f4(float* address, float4 v) {
                  : "memory");
 }
 
+// A lane's partial sums of q = g * gamma and of q * xhat over its chunks.
+template <bool kPacked>
+struct BackwardLaneSums;
+
+template <>
+struct BackwardLaneSums<true> {
+    float2 q = {0.0f, 0.0f};
+    float2 qx = {0.0f, 0.0f};
+    __device__ __forceinline__ float total_q() const { return q.x + q.y; }
+    __device__ __forceinline__ float total_qx() const { return qx.x + qx.y; }
+};
+
+template <>
+struct BackwardLaneSums<false> {
+    float q = 0.0f;
+    float qx = 0.0f;
+    __device__ __forceinline__ float total_q() const { return q; }
+    __device__ __forceinline__ float total_qx() const { return qx; }
+};
+
+// First pass over a chunk: xhat = (u - mean) * rstd, the parameter-gradient
+// accumulators, q = g * gamma and the lane's partial sums of q and q * xhat.
+// Returns xhat in `u` and q in `g`.
+template <bool kParams, bool kPacked>
+__device__ __forceinline__ void backward_first_pass(
+    float4& u, float4& g, float4 gamma, float mean, float rstd,
+    float4& acc_weight, float4& acc_bias, BackwardLaneSums<kPacked>& sums) {
+    if constexpr (kPacked) {
+        const float2 shift = splat2(-mean);
+        const float2 scale = splat2(rstd);
+        const float2 xhat_lo = __fmul2_rn(__fadd2_rn(lo2(u), shift), scale);
+        const float2 xhat_hi = __fmul2_rn(__fadd2_rn(hi2(u), shift), scale);
+        const float2 g_lo = lo2(g);
+        const float2 g_hi = hi2(g);
+        if constexpr (kParams) {
+            acc_weight = join4(__ffma2_rn(g_lo, xhat_lo, lo2(acc_weight)),
+                               __ffma2_rn(g_hi, xhat_hi, hi2(acc_weight)));
+            acc_bias = join4(__fadd2_rn(lo2(acc_bias), g_lo), __fadd2_rn(hi2(acc_bias), g_hi));
+        }
+        const float2 q_lo = __fmul2_rn(g_lo, lo2(gamma));
+        const float2 q_hi = __fmul2_rn(g_hi, hi2(gamma));
+        sums.q = __fadd2_rn(sums.q, __fadd2_rn(q_lo, q_hi));
+        sums.qx = __ffma2_rn(q_lo, xhat_lo, sums.qx);
+        sums.qx = __ffma2_rn(q_hi, xhat_hi, sums.qx);
+        g = join4(q_lo, q_hi);
+        u = join4(xhat_lo, xhat_hi);
+    } else {
+        float4 xhat;
+        xhat.x = (u.x - mean) * rstd;
+        xhat.y = (u.y - mean) * rstd;
+        xhat.z = (u.z - mean) * rstd;
+        xhat.w = (u.w - mean) * rstd;
+        if constexpr (kParams) {
+            acc_weight.x += g.x * xhat.x;
+            acc_weight.y += g.y * xhat.y;
+            acc_weight.z += g.z * xhat.z;
+            acc_weight.w += g.w * xhat.w;
+            acc_bias.x += g.x;
+            acc_bias.y += g.y;
+            acc_bias.z += g.z;
+            acc_bias.w += g.w;
+        }
+        float4 q;
+        q.x = g.x * gamma.x;
+        q.y = g.y * gamma.y;
+        q.z = g.z * gamma.z;
+        q.w = g.w * gamma.w;
+        sums.q += (q.x + q.y) + (q.z + q.w);
+        sums.qx += (q.x * xhat.x + q.y * xhat.y) + (q.z * xhat.z + q.w * xhat.w);
+        g = q;
+        u = xhat;
+    }
+}
+
+// Second pass: grad_x = grad_updated + rstd * (q - mean(q) - xhat * mean(q * xhat)).
+template <bool kPacked>
+__device__ __forceinline__ float4 backward_input_gradient(
+    float4 grad_updated, float4 q, float4 xhat, float rstd, float mean_q, float mean_qx) {
+    if constexpr (kPacked) {
+        const float2 minus_mean_q = splat2(-mean_q);
+        const float2 minus_mean_qx = splat2(-mean_qx);
+        const float2 scale = splat2(rstd);
+        const float2 lo = __ffma2_rn(
+            __ffma2_rn(lo2(xhat), minus_mean_qx, __fadd2_rn(lo2(q), minus_mean_q)), scale,
+            lo2(grad_updated));
+        const float2 hi = __ffma2_rn(
+            __ffma2_rn(hi2(xhat), minus_mean_qx, __fadd2_rn(hi2(q), minus_mean_q)), scale,
+            hi2(grad_updated));
+        return join4(lo, hi);
+    } else {
+        float4 total;
+        total.x = grad_updated.x + rstd * (q.x - mean_q - xhat.x * mean_qx);
+        total.y = grad_updated.y + rstd * (q.y - mean_q - xhat.y * mean_qx);
+        total.z = grad_updated.z + rstd * (q.z - mean_q - xhat.z * mean_qx);
+        total.w = grad_updated.w + rstd * (q.w - mean_q - xhat.w * mean_qx);
+        return total;
+    }
+}
+
 template <int H, typename BranchT, bool kDropout, bool kParams, bool kAligned, int kWarps, int kRows,
-          int kMinCtas = 1, bool kStreamHints = false, typename NormT = float>
+          int kMinCtas = 1, bool kStreamHints = false, typename NormT = float,
+          bool kDynamicRows = false, bool kPacked = false>
 __global__ void __launch_bounds__(kWarps * kWarpSize, kMinCtas)
 rln_backward_kernel(const BackwardParams p) {
     static_assert(H % 128 == 0, "hidden must be a multiple of 128");
@@ -754,8 +970,8 @@ rln_backward_kernel(const BackwardParams p) {
         }
     }
 
-    for (int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRows;
-         first < p.rows; first += stride) {
+    int64_t first = (static_cast<int64_t>(blockIdx.x) * kWarps + warp) * kRows;
+    while (first < p.rows) {
         float4 gy[kRows][V];
         float4 uu[kRows][V];
         float4 gu[kRows][V];
@@ -782,6 +998,15 @@ rln_backward_kernel(const BackwardParams p) {
                 }
             }
         }
+        // claim the next group now; the answer is needed after this group's stores
+        unsigned int ticket = 0u;
+        bool claimed = false;  // warp-uniform
+        if constexpr (kDynamicRows) {
+            claimed = first + stride >= p.dynamic_begin;
+            if (claimed && lane == 0) {
+                ticket = atomicAdd(p.row_counter, static_cast<unsigned int>(kRows));
+            }
+        }
 
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
@@ -791,37 +1016,17 @@ rln_backward_kernel(const BackwardParams p) {
             }
             const float mu = row_mean[r];
             const float rs = row_rstd[r];
-            float sum_q = 0.0f;
-            float sum_qx = 0.0f;
+            BackwardLaneSums<kPacked> sums;
 #pragma unroll
             for (int k = 0; k < V; ++k) {
                 const float4 gamma = load_param<kAligned>(p.weight, lane + k * kWarpSize);
-                float4 xhat;
-                xhat.x = (uu[r][k].x - mu) * rs;
-                xhat.y = (uu[r][k].y - mu) * rs;
-                xhat.z = (uu[r][k].z - mu) * rs;
-                xhat.w = (uu[r][k].w - mu) * rs;
-                const float4 g = gy[r][k];
-                if constexpr (kParams) {
-                    acc_weight[k].x += g.x * xhat.x;
-                    acc_weight[k].y += g.y * xhat.y;
-                    acc_weight[k].z += g.z * xhat.z;
-                    acc_weight[k].w += g.w * xhat.w;
-                    acc_bias[k].x += g.x;
-                    acc_bias[k].y += g.y;
-                    acc_bias[k].z += g.z;
-                    acc_bias[k].w += g.w;
-                }
-                float4 q;
-                q.x = g.x * gamma.x;
-                q.y = g.y * gamma.y;
-                q.z = g.z * gamma.z;
-                q.w = g.w * gamma.w;
-                sum_q += (q.x + q.y) + (q.z + q.w);
-                sum_qx += (q.x * xhat.x + q.y * xhat.y) + (q.z * xhat.z + q.w * xhat.w);
-                gy[r][k] = q;      // reuse registers: weighted gradient
-                uu[r][k] = xhat;   // reuse registers: normalised value
+                // afterwards uu holds the normalised value, gy the weighted gradient
+                backward_first_pass<kParams, kPacked>(
+                    uu[r][k], gy[r][k], gamma, mu, rs,
+                    acc_weight[kParams ? k : 0], acc_bias[kParams ? k : 0], sums);
             }
+            float sum_q = sums.total_q();
+            float sum_qx = sums.total_qx();
 #pragma unroll
             for (int delta = 16; delta > 0; delta >>= 1) {
                 sum_q += __shfl_xor_sync(kFullMask, sum_q, delta);
@@ -832,22 +1037,21 @@ rln_backward_kernel(const BackwardParams p) {
 #pragma unroll
             for (int k = 0; k < V; ++k) {
                 const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
-                float4 total;
-                total.x = gu[r][k].x + rs * (gy[r][k].x - mean_q - uu[r][k].x * mean_qx);
-                total.y = gu[r][k].y + rs * (gy[r][k].y - mean_q - uu[r][k].y * mean_qx);
-                total.z = gu[r][k].z + rs * (gy[r][k].z - mean_q - uu[r][k].z * mean_qx);
-                total.w = gu[r][k].w + rs * (gy[r][k].w - mean_q - uu[r][k].w * mean_qx);
+                float4 total = backward_input_gradient<kPacked>(
+                    gu[r][k], gy[r][k], uu[r][k], rs, mean_q, mean_qx);
                 store_f4<kAligned, kStreamHints>(p.grad_x, chunk, total);
                 if constexpr (kDropout) {
                     const uint32_t n = words[r][k] >> (4 * (lane & 7));
                     // g * keep * scale as one multiply (same bits, see drop_four)
-                    total.x = __fmul_rn(total.x, (n & 1u) ? p.scale : 0.0f);
-                    total.y = __fmul_rn(total.y, (n & 2u) ? p.scale : 0.0f);
-                    total.z = __fmul_rn(total.z, (n & 4u) ? p.scale : 0.0f);
-                    total.w = __fmul_rn(total.w, (n & 8u) ? p.scale : 0.0f);
+                    total = scale_kept<kPacked>(total, n, p.scale);
                 }
                 IO::template store<kAligned, kStreamHints>(p.grad_branch, chunk, total);
             }
+        }
+        if (kDynamicRows && claimed) {
+            first = p.dynamic_begin + static_cast<int64_t>(__shfl_sync(kFullMask, ticket, 0));
+        } else {
+            first += stride;
         }
     }
 

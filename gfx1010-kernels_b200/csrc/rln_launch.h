@@ -40,6 +40,13 @@ struct ForwardTune {
     static constexpr int kMinCtas =
         H <= 256 ? 6 : (H <= 384 ? 16 : (H <= 512 ? 12 : (H <= 768 ? 18 : 16)));
     static constexpr bool kPersistent = false;
+    // Two-wide fp32 arithmetic (kPacked of the kernels): H = 384 runs 32 warps
+    // per SM on 64 registers each and is the one width whose forward gains from
+    // the halved instruction count (same board, back to back: 174,762 rows
+    // 0.1574 -> 0.1466 ms, 32,768 rows 0.0318 -> 0.0299 ms); H = 512 and the
+    // sub-warp widths do not move, H = 768 / 1024 lose 4-5 % (more spills under
+    // their 96-register budget).
+    static constexpr bool kPacked = H == 384;
 };
 
 // The backward grid is persistent (register-resident parameter-gradient
@@ -88,6 +95,47 @@ cudaError_t launch_dependent(
 // Remembers a failing CUDA call for rln_sm100_last_cuda_error (per thread) and
 // returns RLN_ERR_CUDA.
 int record_cuda_error(cudaError_t error);
+
+// One backward call as it crosses the C ABI (every backward entry point fills
+// this and goes through the same two functions, so their argument rules cannot
+// drift apart).
+struct BackwardCall {
+    const float* grad_updated;
+    const void* grad_normalized;
+    const float* updated;
+    const float* weight;
+    const float* mean;
+    const float* rstd;
+    const uint32_t* dropout_mask;
+    float* grad_x;
+    void* grad_branch;
+    float* grad_parameters;     // NULL = parameter gradients not requested
+    bool parameters_required;   // entry points that exist to reduce them
+    int64_t rows;
+    int32_t hidden;
+    int32_t branch_dtype;
+    int32_t normalized_dtype;
+    int32_t dropout_active;
+    float dropout_p;
+};
+
+// RLN_OK or the RLN_ERR_* code of the first violated rule; on RLN_OK
+// *vector_ok says whether the 16-byte-vector kernels apply.
+int check_backward_call(const BackwardCall& call, bool* vector_ok);
+
+// Zeroing kernel (fast path), backward kernel and, for `deterministic`, the
+// fixed-order reduction over the partials in `scratch`; a scratch that is
+// missing, misaligned or too small for the partials returns `scratch_error`.
+// Without `deterministic` the scratch is not used.
+int launch_backward_call(
+    const BackwardCall& call,
+    bool vector_ok,
+    int sm_count,
+    bool deterministic,
+    void* scratch,
+    int64_t scratch_bytes,
+    int scratch_error,
+    cudaStream_t stream);
 
 // Number of CTAs of the persistent backward grid (pure function of its
 // arguments; also the number of [2, hidden] partials in deterministic mode).

@@ -271,6 +271,10 @@ RLN_API int rln_sm100_backward(
  *     different streams, or different host threads -- race on it and give
  *     wrong grad_parameters.  Serialise calls per device.
  *   - grad_parameters is required (this is the variant that reduces them).
+ *   - The cached scratch address belongs to the device's primary context.  It
+ *     does not survive cudaDeviceReset (or any other teardown of that context):
+ *     do not reset a device while this library is loaded and this entry point
+ *     is still going to be called on it.
  *
  * Arguments as in rln_sm100_backward.
  */

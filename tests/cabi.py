@@ -107,7 +107,8 @@ def backward(grad_updated, grad_normalized, updated, weight, mean, rstd, mask, d
         )
         assert workspace_bytes >= 0, status_text(workspace_bytes)
         if workspace_bytes:
-            workspace = torch.empty(workspace_bytes // 4, device=device)
+            # non-zero garbage: the call itself has to clear what it needs cleared
+            workspace = torch.full((workspace_bytes // 4,), 123.0, device=device)
     status = library().rln_sm100_backward(
         _ptr(grad_updated), _ptr(grad_normalized), _ptr(updated), _ptr(weight),
         _ptr(mean), _ptr(rstd), _ptr(mask) if active else None,

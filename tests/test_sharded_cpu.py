@@ -192,3 +192,91 @@ def test_single_process_step_needs_no_process_group():
     with pytest.raises(ValueError):
         sharded_forward_backward(x, branch[:3], weight, bias, grad_updated, grad_normalized,
                                  row_base=0, compute=oracle_compute)
+
+
+def worker_fewer_rows_than_ranks(rank, world, port, out_dir):
+    """Two rows over three ranks: one rank owns nothing, skips the compute,
+    contributes zeros and still joins the all-reduce (nobody waits for it)."""
+    init(rank, world, port, timeout=20)
+    try:
+        x, branch, weight, bias, grad_updated, grad_normalized = global_problem()
+        rows = 2
+        begin, end = shard_bounds(rows, world, rank)
+        calls = []
+
+        def counting_compute(*args):
+            calls.append(1)
+            return oracle_compute(*args)
+
+        result = sharded_forward_backward(
+            x[begin:end], branch[begin:end], weight, bias,
+            grad_updated[begin:end], grad_normalized[begin:end],
+            row_base=begin, dropout_p=P, eps=EPS, training=True, seed=SEED, offset=OFFSET,
+            compute=counting_compute,
+        )
+        torch.save(
+            {"begin": begin, "end": end, "calls": len(calls), "updated": result.updated,
+             "mask": result.mask, "grad_weight": result.grad_weight,
+             "grad_bias": result.grad_bias},
+            Path(out_dir) / f"rank{rank}.pt",
+        )
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rank_without_rows_still_joins_the_all_reduce(tmp_path):
+    world = 3
+    mp.spawn(worker_fewer_rows_than_ranks, args=(world, free_port(), str(tmp_path)),
+             nprocs=world, join=True)
+    pieces = [torch.load(tmp_path / f"rank{rank}.pt") for rank in range(world)]
+    empty = [piece for piece in pieces if piece["begin"] == piece["end"]]
+    assert len(empty) == 1 and empty[0]["calls"] == 0
+    assert empty[0]["updated"].shape == (0, HIDDEN) and empty[0]["mask"].numel() == 0
+    x, branch, weight, bias, grad_updated, grad_normalized = global_problem()
+    whole = oracle_compute(x[:2], branch[:2], weight, bias, grad_updated[:2], grad_normalized[:2],
+                           P, EPS, True, SEED, OFFSET, 0)
+    for piece in pieces:
+        torch.testing.assert_close(piece["grad_weight"], whole[4][0], rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(piece["grad_bias"], whole[4][1], rtol=1e-5, atol=1e-5)
+
+
+def worker_async_chain(rank, world, port, out_dir):
+    """Three steps with async_op=True, each handed the previous step's handle:
+    the sums of every step must be the synchronous ones."""
+    init(rank, world, port)
+    try:
+        x, branch, weight, bias, grad_updated, grad_normalized = global_problem()
+        begin, end = shard_bounds(ROWS, world, rank)
+        shard = (x[begin:end], branch[begin:end], weight, bias,
+                 grad_updated[begin:end], grad_normalized[begin:end])
+        pending, handles = None, []
+        for step in range(3):
+            pending = sharded_forward_backward(
+                *shard, row_base=begin, dropout_p=P, eps=EPS, seed=SEED, offset=OFFSET + 4 * step,
+                compute=oracle_compute, async_op=True, previous=pending,
+            )
+            handles.append(pending)
+        results = [handle.wait() for handle in handles]
+        assert all(handle.is_completed() for handle in handles)
+        reference = [
+            sharded_forward_backward(
+                *shard, row_base=begin, dropout_p=P, eps=EPS, seed=SEED, offset=OFFSET + 4 * step,
+                compute=oracle_compute,
+            )
+            for step in range(3)
+        ]
+        same = all(
+            torch.equal(a.grad_weight, b.grad_weight) and torch.equal(a.grad_bias, b.grad_bias)
+            and torch.equal(a.mask, b.mask)
+            for a, b in zip(results, reference)
+        )
+        distinct = not torch.equal(results[0].mask, results[1].mask)
+        (Path(out_dir) / f"rank{rank}.txt").write_text(f"{same} {distinct}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_async_steps_chained_through_previous_give_the_synchronous_sums(tmp_path):
+    mp.spawn(worker_async_chain, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    for rank in range(2):
+        assert (tmp_path / f"rank{rank}.txt").read_text() == "True True"
