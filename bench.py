@@ -695,7 +695,7 @@ def run_strong_c5(args, rank, world, device):
     return record
 
 
-def public_api_device_step_ms(runner, steps, first):
+def public_api_device_step_ms(runner, steps):
     """Mean milliseconds of the step through the public call --
     ``residual_layer_norm(implementation="gfx1010")`` + ``torch.autograd.grad`` --
     on this rank's device-resident tensors (no collective), CUDA events."""
@@ -703,7 +703,6 @@ def public_api_device_step_ms(runner, steps, first):
 
     leaves = [t.detach().clone().requires_grad_(True)
               for t in (runner.x, runner.branch, runner.weight, runner.bias)]
-    generator = torch.cuda.default_generators[runner.device.index]
 
     def one(index):
         updated, normalized = residual_layer_norm(
@@ -713,7 +712,6 @@ def public_api_device_step_ms(runner, steps, first):
         return torch.autograd.grad(
             (updated, normalized), leaves, (runner.grad_updated, runner.grad_normalized))
 
-    del generator, first
     for index in range(10):
         one(index)
     torch.cuda.synchronize()
@@ -738,20 +736,248 @@ def public_api_device_step_ms(runner, steps, first):
     return start.elapsed_time(stop) / steps
 
 
-@@NATIVE@@
+def run_native_arm(args, rank, local_rank, world):
+    import torch.distributed as dist
+
+    from gfx1010_kernels import residual_layer_norm, residual_layer_norm_status
+    from gfx1010_kernels import sharded
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py --impl native needs a CUDA device (no CPU fallback)")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    status = residual_layer_norm_status(device)
+    if not status.available:
+        raise RuntimeError(f"native backend unavailable: {status.reason}")
+    if world > 1:
+        # NCCL on a high-priority stream (see sharded.high_priority_nccl_options),
+        # and a short timeout: a rank that stops calling collectives must surface
+        # as an error within minutes, not hold the GPUs for the default ten.
+        sharded.init_sharded_process_group(
+            device, timeout=datetime.timedelta(seconds=180),
+            high_priority=not args.default_priority_collectives,
+        )
+
+    rows, hidden, branch_dtype, dropout_p, normalized_dtype = workload(args.workload)
+    branch_bytes = 4 if branch_dtype == torch.float32 else 2
+    normalized_bytes = 4 if normalized_dtype == torch.float32 else 2
+    runner = ShardRunner(args.workload, rows, rank * rows, rank, device, world)
+    regions = 3 if args.kernel_only else args.regions
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    # warm-up: W steps, then as many more as bring the loaded span to about a second
+    # (clock settling + clock samples).  The count is agreed between the ranks --
+    # every step contains a collective, so all ranks must run the same number.
+    warm_begin = time.perf_counter()
+    base = max(args.warmup, 3)
+    runner.warm(base, 0)
+    warmup_actual = base
+    if not args.kernel_only:
+        probe_begin = time.perf_counter()
+        runner.warm(10, base)    # timed probe (the first steps above carry one-time set-up)
+        warmup_actual += 10
+        per_step = (time.perf_counter() - probe_begin) / 10
+        extra = int(min(5000, 1.0 / max(per_step, 1e-6)))
+        if world > 1:
+            agreed = torch.tensor([extra], device=device, dtype=torch.int64)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+            extra = int(agreed.item())
+        runner.warm(extra, warmup_actual)
+        warmup_actual += extra
+
+    run_step = None
+    if args.cuda_graph:
+        if world > 1:
+            raise RuntimeError("--cuda-graph is a single-GPU mode")
+        # One step (forward, zeroing kernel, backward and the allocator's work)
+        # recorded once; every replay re-runs it with the recorded Philox offset.
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            runner.step(warmup_actual)
+        runner.pending = None
+
+        def run_step(index):
+            graph.replay()
+
+        for _ in range(10):
+            run_step(0)
+
+    timed_begin = time.perf_counter()
+    region_ms, next_index = runner.timed_regions(regions, args.steps, warmup_actual, run_step)
+    timed_end = time.perf_counter()
+    # per-kernel durations: same steps, same buffers, right after the timed regions
+    forward_ms, backward_ms = runner.kernel_pass(min(args.steps, 100), next_index)
+    next_index += min(args.steps, 100)
+    clocks = sampler.summary([
+        ("timed regions", timed_begin, timed_end),
+        ("warm-up + timed regions (the timed regions hold fewer than two samples)",
+         warm_begin, timed_end),
+    ])
+
+    check = None
+    if world > 1:
+        check = sharded_check(runner, rank, world, rows * world, 4 * (next_index + 7))
+
+    public_ms = None
+    if not args.kernel_only:
+        public_ms = public_api_device_step_ms(runner, min(args.steps, 100))
+
+    # end-to-end: pinned host inputs -> device -> fwd+bwd -> results back to host
+    if args.kernel_only:
+        e2e = None
+    else:
+        e2e = run_end_to_end(
+            args, device, runner.host, runner.weight, runner.bias, dropout_p, world,
+            residual_layer_norm, normalized_dtype,
+        )
+    sampler.stop()
+    del runner
+    torch.cuda.empty_cache()
+
+    strong = None
+    if (args.workload == "h768_64Mi" and not args.no_strong_c5 and not args.kernel_only
+            and not args.cuda_graph):
+        strong = run_strong_c5(args, rank, world, device)
+
+    region_ms = max_over_ranks(region_ms, device, world)
+    has_public = public_ms is not None
+    stats = [forward_ms, backward_ms, public_ms or 0.0]
+    if e2e is not None:
+        stats += [e2e["ms"], e2e["public_ms"], e2e["copy_ms"]]
+    stats = max_over_ranks(stats, device, world)
+    forward_ms, backward_ms, public_ms = stats[:3]
+
+    failed = False
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        total_rows = rows * world
+        elapsed_ms = statistics.median(region_ms)
+        value = total_rows * args.steps / (elapsed_ms * 1e-3)
+        fwd_row = forward_bytes_per_row(hidden, branch_bytes, dropout_p > 0, normalized_bytes)
+        bwd_row = backward_bytes_per_row(hidden, branch_bytes, dropout_p > 0, normalized_bytes)
+        fwd_bytes = fwd_row * rows
+        bwd_bytes = bwd_row * rows
+        fwd_gbs = fwd_bytes / (forward_ms * 1e-3) / 1e9
+        bwd_gbs = bwd_bytes / (backward_ms * 1e-3) / 1e9
+        step_gbs = (fwd_bytes + bwd_bytes) * world * args.steps / (elapsed_ms * 1e-3) / 1e9
+        cpu = None
+        if world == 1 and not args.kernel_only:
+            cpu = cpu_baseline_record(args.workload)
+        line = {
+            "metric": METRIC,
+            "value": value,
+            "value_min": total_rows * args.steps / (max(region_ms) * 1e-3),
+            "value_max": total_rows * args.steps / (min(region_ms) * 1e-3),
+            "unit": UNIT,
+            "n_gpus": world,
+            "steps": args.steps,
+            "regions": regions,
+            "timing": f"median of {regions} back-to-back regions of {args.steps} steps, each "
+                      "fenced (pending all-reduce, device, barrier) and timed with CUDA events, "
+                      "max over ranks per region",
+            "warmup": args.warmup,
+            "warmup_actual": warmup_actual,
+            "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f32",
+            "data": "synthetic",
+            "config": workload_config(args.workload, world),
+            "launch": "one step recorded into a CUDA graph, replayed (fixed Philox offset)"
+            if args.cuda_graph else
+            "eager: gfx1010_kernels.sharded.sharded_forward_backward(async_op=True, "
+            "previous=...) per step (three kernel launches through the extension)",
+            "hbm_gbs_step": step_gbs,
+            "hbm_frac_of_8000": step_gbs / (HBM_SPEC_GBS * world),
+            "hbm_frac_of_measured": step_gbs / (peak * world),
+            "kernels": {
+                "forward": {"ms": forward_ms, "gbs": fwd_gbs, "bytes_per_row": fwd_row,
+                            "includes": "wait for the previous step's all-reduce (N > 1)"},
+                "backward": {"ms": backward_ms, "gbs": bwd_gbs, "bytes_per_row": bwd_row,
+                             "includes": "the zeroing kernel of the [2,H] buffer"},
+            },
+            "roofline": {
+                "kernel": "rln_backward_kernel",
+                "bound": "hbm",
+                "achieved": bwd_gbs,
+                "peak": peak,
+                "peak_kind": f"{peak_kind} copy bandwidth (burst)",
+                "unit": "GB/s",
+                "frac": bwd_gbs / peak,
+                "frac_of_8000": bwd_gbs / HBM_SPEC_GBS,
+                "traffic": NCU_BACKWARD_TRAFFIC_BYTES.get(args.workload),
+                "traffic_unit": "bytes per launch (ncu dram read + write)",
+                "algorithmic_bytes_per_launch": bwd_bytes,
+                "timing": "CUDA events around each backward launch, in a pass of the same "
+                          "steps right after the timed regions",
+            },
+            "cpu_baseline": cpu,
+            "public_api_device_value": total_rows / (public_ms * 1e-3) if has_public else None,
+            "public_api_device_path": "residual_layer_norm(implementation='gfx1010') + "
+                                      "torch.autograd.grad on the same device-resident tensors "
+                                      "(C++ autograd node, no collective), CUDA events",
+            "e2e": None,
+            "sharded_check": check,
+            "strong_c5": strong,
+            "gpu_launches": 3 * args.steps * regions,  # forward, zeroing kernel, backward
+            "gpu_launches_per_step": 3,
+            "clocks": clocks,
+        }
+        if e2e is not None:
+            e2e_ms, e2e_public_ms, copy_ms = stats[3:6]
+            line["e2e"] = {
+                "value": total_rows * e2e["steps"] / (e2e_ms * 1e-3),
+                "unit": UNIT,
+                "h2d_bytes_per_step": e2e["h2d"],
+                "d2h_bytes_per_step": e2e["d2h"],
+                "steps": e2e["steps"],
+                "path": "one C-ABI call per step on pinned host buffers "
+                        "(rln_sm100_host_forward_backward_enqueue via "
+                        "gfx1010_kernels.host_pipeline, wait=False): chunked copy-in / fwd+bwd "
+                        "kernels / copy-out on three streams, two output sets, at most two "
+                        "steps in flight (rln_sm100_host_pipeline_wait_step before a set is "
+                        "reused), every step landed before the host clock stops",
+                "public_api_value": total_rows * e2e["steps"] / (e2e_public_ms * 1e-3),
+                "public_api_path": "pinned host -> device copies, residual_layer_norm("
+                                   "implementation='gfx1010') + torch.autograd.grad, results "
+                                   "copied to pinned host, one stream",
+                "copy_ceiling_value": total_rows * e2e["steps"] / (copy_ms * 1e-3),
+                "copy_ceiling_path": "the step's host->device and device->host bytes only, as "
+                                     "whole-tensor pinned copies on two streams, no kernels, "
+                                     "all ranks at once",
+            }
+            line["e2e"]["fraction_of_copy_ceiling"] = (
+                line["e2e"]["value"] / line["e2e"]["copy_ceiling_value"])
+        print(json.dumps(line), flush=True)
+        checks = [check] + ([strong.get("sharded_check")] if strong else [])
+        failed = any(entry is not None and not entry["ok"] for entry in checks)
+    if world > 1:
+        flag = torch.tensor([1 if failed else 0], device=device)
+        dist.broadcast(flag, 0)
+        failed = bool(flag.item())
+        dist.barrier()
+        dist.destroy_process_group()
+    return 3 if failed else 0
 
 
 def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_layer_norm,
                    normalized_dtype=torch.float32):
     """The same step with host buffers on both sides, two ways:
 
-    ``pipeline``    one C-ABI call (rln_sm100_host_forward_backward through
-                    gfx1010_kernels.host_pipeline.HostPipeline): chunked copy-in /
-                    kernels / copy-out overlapped on three streams;
+    ``pipeline``    one C-ABI call per step (rln_sm100_host_forward_backward_enqueue
+                    through gfx1010_kernels.host_pipeline.HostPipeline): chunked
+                    copy-in / kernels / copy-out overlapped on three streams, steps
+                    double-buffered so that consecutive steps overlap too;
     ``public_api``  pinned host -> device copies, gfx1010_kernels.residual_layer_norm
                     (implementation='gfx1010') + torch.autograd.grad, results copied
                     back to pinned host, all on one stream.
-    Both timed regions contain every host<->device byte of a step.
+    Both timed regions contain every host<->device byte of a step.  A third leg
+    (``copy``) moves the same bytes and launches nothing: the input tensors as
+    whole pinned copies on one stream, the result tensors on another, on all
+    ranks at once -- the ceiling the host link sets for this step on this box.
     """
     import torch.distributed as dist
 
@@ -764,6 +990,7 @@ def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_
     pipeline = HostPipeline(hidden, branch_h.dtype, chunk_rows=8192, depth=3, device=device,
                             normalized_dtype=normalized_dtype)
     outputs = pipeline.allocate_outputs(x_h.shape)
+    second_outputs = pipeline.allocate_outputs(x_h.shape)
     out_updated, out_normalized, out_grad_x, out_grad_branch, out_grad_params = outputs
     weight_leaf = weight.detach().clone().requires_grad_(True)
     bias_leaf = bias.detach().clone().requires_grad_(True)
@@ -772,16 +999,32 @@ def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_
     rank = dist.get_rank() if world > 1 else 0
     counter = [0]
 
+    # Double-buffered consumer: step i fills output set i % 2 while set (i - 1) % 2
+    # -- complete once wait(step=...) has returned -- belongs to the caller.  At
+    # most two steps are in flight, and the second one's first chunks are copied
+    # in while the first one's last chunks are computed and copied out.
+    output_sets = (outputs, second_outputs)
+    in_flight = []          # (pipeline step number, output set) of enqueued steps
+
+    def land(limit):
+        """Wait until at most ``limit`` steps are in flight; reduce what landed."""
+        while len(in_flight) > limit:
+            number, landed = in_flight.pop(0)
+            pipeline.wait(step=number)
+            if world > 1:
+                parameters = landed[4].to(device, non_blocking=True)
+                dist.all_reduce(parameters)
+                landed[4].copy_(parameters)
+
     def pipeline_step():
         counter[0] += 1
+        land(1)     # the set about to be refilled was consumed two steps ago
+        target = output_sets[counter[0] % 2]
         pipeline.forward_backward(
             x_h, branch_h, weight_h, bias_h, gu_h, gy_h, dropout_p, EPS, True,
-            seed=0, offset=4 * counter[0], row_base=rank * rows, out=outputs,
+            seed=0, offset=4 * counter[0], row_base=rank * rows, out=target, wait=False,
         )
-        if world > 1:
-            parameters = out_grad_params.to(device, non_blocking=True)
-            dist.all_reduce(parameters)
-            out_grad_params.copy_(parameters)
+        in_flight.append((pipeline.steps_enqueued(), target))
 
     def public_api_step():
         x = x_h.to(device, non_blocking=True).requires_grad_(True)
@@ -808,6 +1051,7 @@ def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_
     def timed(step, steps):
         for _ in range(2):
             step()
+        land(0)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
@@ -815,17 +1059,34 @@ def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_
         begin = time.perf_counter()
         for _ in range(steps):
             step()
+        land(0)     # every enqueued step has landed in host memory (and is reduced)
         torch.cuda.synchronize()
         elapsed = (time.perf_counter() - begin) * 1e3
         if world > 1:
             dist.barrier()
         return elapsed
 
+    in_stream = torch.cuda.Stream(device)
+    out_stream = torch.cuda.Stream(device)
+    host_inputs = (x_h, branch_h, gu_h, gy_h)
+    device_inputs = [torch.empty_like(t, device=device) for t in host_inputs]
+    device_outputs = [torch.empty_like(t, device=device) for t in outputs[:4]]
+
+    def copy_step():
+        with torch.cuda.stream(in_stream):
+            for target, source in zip(device_inputs, host_inputs):
+                target.copy_(source, non_blocking=True)
+        with torch.cuda.stream(out_stream):
+            for target, source in zip(outputs[:4], device_outputs):
+                target.copy_(source, non_blocking=True)
+
     steps = max(2, min(args.steps, 5))
     pipeline_ms = timed(pipeline_step, steps)
     public_ms = timed(public_api_step, steps)
+    copy_ms = timed(copy_step, steps)
     pipeline.close()
-    return {"ms": pipeline_ms, "public_ms": public_ms, "steps": steps, "h2d": h2d, "d2h": d2h}
+    return {"ms": pipeline_ms, "public_ms": public_ms, "copy_ms": copy_ms, "steps": steps,
+            "h2d": h2d, "d2h": d2h}
 
 
 def main(argv=None):
@@ -835,24 +1096,22 @@ def main(argv=None):
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), default="h768_64Mi")
+    parser.add_argument("--regions", type=int, default=REGIONS,
+                        help="back-to-back timed regions of K steps; the median is reported")
+    parser.add_argument("--no-strong-c5", action="store_true",
+                        help="skip the strong-scaling record (the [64,4096,1024] batch split "
+                             "over the GPUs), which the headline workload's run appends")
     parser.add_argument("--cuda-graph", action="store_true",
                         help="N = 1: record one step into a CUDA graph and time its replays "
                              "(what a caller does for launch-bound shapes)")
     parser.add_argument("--default-priority-collectives", action="store_true",
                         help="N > 1: run NCCL on a default-priority stream (A/B switch)")
     parser.add_argument(
-        "--kernel-events-in-loop",
-        action="store_true",
-        help="record the per-kernel CUDA events inside the K timed steps instead of in a "
-             "pass of their own right after them (an event between two kernels keeps the "
-             "second from being scheduled while the first drains, which slows the step)",
-    )
-    parser.add_argument(
         "--kernel-only",
         action="store_true",
-        help="profiling mode: exactly W warm-up steps, no clock-settling warm-up, no "
-             "end-to-end leg and no CPU baseline (few launches, so that a profiler "
-             "capture of this command ends quickly)",
+        help="profiling mode: exactly W warm-up steps, no clock-settling warm-up, three "
+             "timed regions, no end-to-end leg and no CPU baseline (few launches, so that "
+             "a profiler capture of this command ends quickly)",
     )
     args = parser.parse_args(argv)
 

@@ -19,6 +19,7 @@ Usage: ``python build.py [--force] [--verbose]``
 from __future__ import annotations
 
 import argparse
+import hashlib
 import os
 import shutil
 import subprocess
@@ -93,11 +94,32 @@ def _host_compiler() -> str:
     raise RuntimeError("g++ was not found")
 
 
+def _digest(sources) -> str:
+    digest = hashlib.sha256()
+    for source in sources:
+        digest.update(str(Path(source).name).encode())
+        digest.update(Path(source).read_bytes())
+    return digest.hexdigest()
+
+
+def _stamp_path(target: Path) -> Path:
+    return OBJECTS / (target.name + ".sha256")
+
+
 def _newer(target: Path, sources) -> bool:
-    if not target.exists():
+    """True when ``target`` was built from exactly these ``sources``.  Decided by
+    a content hash recorded at build time, not by timestamps: a copy of the tree
+    (to another machine, out of an archive) keeps its binaries valid and a
+    source edit always invalidates them, whatever the copy did to the mtimes."""
+    stamp = _stamp_path(target)
+    if not target.exists() or not stamp.exists():
         return False
-    stamp = target.stat().st_mtime
-    return all(Path(source).stat().st_mtime <= stamp for source in sources)
+    return stamp.read_text().strip() == _digest(sources)
+
+
+def _record(target: Path, sources) -> None:
+    OBJECTS.mkdir(exist_ok=True)
+    _stamp_path(target).write_text(_digest(sources) + "\n")
 
 
 def _run(command, verbose):
@@ -132,6 +154,7 @@ def build_kernel_library(force=False, verbose=False) -> Path:
         if not force and _newer(target, [source] + headers):
             return target
         _run([nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-I", CSRC, "-c", source, "-o", target], verbose)
+        _record(target, [source] + headers)
         return target
 
     with ThreadPoolExecutor(max_workers=len(sources)) as pool:
@@ -150,6 +173,7 @@ def build_kernel_library(force=False, verbose=False) -> Path:
         ],
         verbose,
     )
+    _record(KERNEL_LIBRARY, sources + headers)
     return KERNEL_LIBRARY
 
 
@@ -159,8 +183,10 @@ def build_extension(force=False, verbose=False) -> Path:
 
     cuda = _cuda_home()
     source = CSRC / "rln_bindings.cpp"
-    dependencies = [source, INCLUDE / "rln_sm100.h", KERNEL_LIBRARY, Path(__file__)]
-    if not force and _newer(EXTENSION, dependencies):
+    # (the extension links the kernel library by name and calls it through the
+    # C ABI of the header, so the library's content is not a dependency)
+    dependencies = [source, INCLUDE / "rln_sm100.h", Path(__file__)]
+    if not force and KERNEL_LIBRARY.exists() and _newer(EXTENSION, dependencies):
         return EXTENSION
     torch_library = Path(torch.__file__).resolve().parent / "lib"
     includes = []
@@ -197,6 +223,7 @@ def build_extension(force=False, verbose=False) -> Path:
     ]
     _run(command, verbose)
     _check_dynamic_libstdcxx(EXTENSION)
+    _record(EXTENSION, dependencies)
     return EXTENSION
 
 

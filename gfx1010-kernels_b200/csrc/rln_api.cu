@@ -180,8 +180,13 @@ int forward_launch(
     params.threshold = dropout_threshold(dropout_p);
     params.seed_lo = static_cast<uint32_t>(seed);
     params.seed_hi = static_cast<uint32_t>(seed >> 32);
-    params.offset_lo = static_cast<uint32_t>(offset);
-    params.offset_hi = static_cast<uint32_t>(offset >> 32);
+    // The generator's offset counts 32-bit words; a Philox call yields four, so
+    // the counter's low half is the block index offset / 4 -- the convention of
+    // torch's (and the reference's hipRAND) generators, under which a later
+    // random op, whose offset is at least four words further on, can never land
+    // on a counter this call used.
+    params.offset_lo = static_cast<uint32_t>(offset >> 2);
+    params.offset_hi = static_cast<uint32_t>(offset >> 34);
     params.device_seed = device_seed;
     params.device_offset = device_offset;
     params.device_offset_extra = device_seed != nullptr ? offset : 0;

@@ -27,6 +27,8 @@ __global__ void accumulate_parameters_kernel(
     }
 }
 
+constexpr int kStepsTracked = 8;
+
 struct Slot {
     float* x = nullptr;
     void* branch = nullptr;
@@ -63,6 +65,12 @@ struct RlnHostPipeline {
     float* weight = nullptr;
     float* bias = nullptr;
     float* total = nullptr;
+    int64_t chunks_enqueued = 0;  // position in the slot ring; runs on across calls
+    // Completion of the most recent steps: step n (1-based count of enqueued
+    // steps) has landed once both events of entry n % kStepsTracked fired.
+    int64_t steps_enqueued = 0;
+    cudaEvent_t step_out[kStepsTracked] = {};       // last chunk copied out
+    cudaEvent_t step_compute[kStepsTracked] = {};   // parameter gradients copied out
     Slot slots[kMaxDepth];
 };
 
@@ -91,6 +99,10 @@ void release(RlnHostPipeline* p) {
         if (slot.computed) cudaEventDestroy(slot.computed);
         if (slot.drained) cudaEventDestroy(slot.drained);
     }
+    for (int n = 0; n < kStepsTracked; ++n) {
+        if (p->step_out[n]) cudaEventDestroy(p->step_out[n]);
+        if (p->step_compute[n]) cudaEventDestroy(p->step_compute[n]);
+    }
     cudaFree(p->weight);
     cudaFree(p->bias);
     cudaFree(p->total);
@@ -100,14 +112,18 @@ void release(RlnHostPipeline* p) {
     delete p;
 }
 
-#define RLN_TRY(call)                      \
-    do {                                   \
-        if ((call) != cudaSuccess) {       \
-            return false;                  \
-        }                                  \
+// Returns the first failing call's error as it is (the caller releases what was
+// allocated so far, which issues further CUDA calls: asking the runtime for its
+// last error after that could name a different failure).
+#define RLN_TRY(call)                                  \
+    do {                                               \
+        const cudaError_t rln_try_error = (call);      \
+        if (rln_try_error != cudaSuccess) {            \
+            return rln_try_error;                      \
+        }                                              \
     } while (0)
 
-bool allocate(RlnHostPipeline* p) {
+cudaError_t allocate(RlnHostPipeline* p) {
     const size_t elements = static_cast<size_t>(p->chunk_rows) * p->hidden;
     const size_t branch_bytes = elements * (p->branch_dtype == RLN_DTYPE_FLOAT32 ? 4 : 2);
     const size_t normalized_bytes = elements * (p->normalized_dtype == RLN_DTYPE_FLOAT32 ? 4 : 2);
@@ -117,6 +133,10 @@ bool allocate(RlnHostPipeline* p) {
     RLN_TRY(cudaMalloc(&p->weight, p->hidden * sizeof(float)));
     RLN_TRY(cudaMalloc(&p->bias, p->hidden * sizeof(float)));
     RLN_TRY(cudaMalloc(&p->total, 2 * p->hidden * sizeof(float)));
+    for (int n = 0; n < kStepsTracked; ++n) {
+        RLN_TRY(cudaEventCreateWithFlags(&p->step_out[n], cudaEventDisableTiming));
+        RLN_TRY(cudaEventCreateWithFlags(&p->step_compute[n], cudaEventDisableTiming));
+    }
     for (int s = 0; s < p->depth; ++s) {
         Slot& slot = p->slots[s];
         RLN_TRY(cudaMalloc(&slot.x, elements * 4));
@@ -138,7 +158,7 @@ bool allocate(RlnHostPipeline* p) {
         RLN_TRY(cudaEventCreateWithFlags(&slot.computed, cudaEventDisableTiming));
         RLN_TRY(cudaEventCreateWithFlags(&slot.drained, cudaEventDisableTiming));
     }
-    return true;
+    return cudaSuccess;
 }
 
 }  // namespace
@@ -185,9 +205,11 @@ extern "C" int rln_sm100_host_pipeline_create(
     p->chunk_rows = chunk_rows;
     p->depth = depth;
     p->workspace_bytes = workspace_bytes;
-    if (!allocate(p)) {
+    const cudaError_t allocation_error = allocate(p);
+    if (allocation_error != cudaSuccess) {
         release(p);
-        return rln::record_cuda_error(cudaGetLastError());
+        (void)cudaGetLastError();  // clear the runtime's sticky copy of the same failure
+        return rln::record_cuda_error(allocation_error);
     }
     *pipeline = p;
     return RLN_OK;
@@ -266,8 +288,14 @@ int enqueue_step(
     const char* grad_normalized_bytes = static_cast<const char*>(grad_normalized);
     char* normalized_bytes = static_cast<char*>(normalized);
 
-    for (int s = 0; s < p->depth; ++s) {
-        p->slots[s].used = false;
+    // The slot ring and its events carry over from the previous call: a step
+    // enqueued behind another one (rln_sm100_host_forward_backward_enqueue) reuses
+    // a slot only after that slot's kernels ran and its results left.
+    const int tracked = static_cast<int>((p->steps_enqueued + 1) % kStepsTracked);
+    if (p->steps_enqueued >= kStepsTracked) {
+        // the completion entry is reused: the step that held it must have landed
+        RLN_TRY(cudaEventSynchronize(p->step_out[tracked]));
+        RLN_TRY(cudaEventSynchronize(p->step_compute[tracked]));
     }
     RLN_TRY(cudaMemcpyAsync(
         p->weight, weight, hidden * sizeof(float), cudaMemcpyHostToDevice, p->stream_compute));
@@ -279,7 +307,8 @@ int enqueue_step(
         const int64_t count = rows - begin < p->chunk_rows ? rows - begin : p->chunk_rows;
         const size_t elements = static_cast<size_t>(count) * hidden;
         const size_t first = static_cast<size_t>(begin) * hidden;
-        Slot& slot = p->slots[chunk_index % p->depth];
+        Slot& slot = p->slots[p->chunks_enqueued % p->depth];
+        ++p->chunks_enqueued;
 
         // copy in (the slot's inputs are free once its previous kernels ran)
         if (slot.used) {
@@ -342,10 +371,93 @@ int enqueue_step(
     RLN_TRY(cudaMemcpyAsync(
         grad_parameters, p->total, 2 * hidden * sizeof(float), cudaMemcpyDeviceToHost,
         p->stream_compute));
+    RLN_TRY(cudaEventRecord(p->step_out[tracked], p->stream_out));
+    RLN_TRY(cudaEventRecord(p->step_compute[tracked], p->stream_compute));
+    ++p->steps_enqueued;
     return RLN_OK;
 }
 
 }  // namespace
+
+namespace {
+
+// Waits for everything the pipeline has enqueued; first failure wins.
+int drain(RlnHostPipeline* p) {
+    const cudaError_t drained_in = cudaStreamSynchronize(p->stream_in);
+    const cudaError_t drained_compute = cudaStreamSynchronize(p->stream_compute);
+    const cudaError_t drained_out = cudaStreamSynchronize(p->stream_out);
+    for (const cudaError_t error : {drained_in, drained_compute, drained_out}) {
+        if (error != cudaSuccess) {
+            return rln::record_cuda_error(error);
+        }
+    }
+    return RLN_OK;
+}
+
+}  // namespace
+
+extern "C" int rln_sm100_host_forward_backward_enqueue(
+    RlnHostPipeline* p,
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    const float* grad_updated,
+    const void* grad_normalized,
+    float* updated,
+    void* normalized,
+    float* grad_x,
+    void* grad_branch,
+    float* grad_parameters,
+    int64_t rows,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    uint64_t seed,
+    uint64_t offset,
+    int64_t row_base,
+    int32_t deterministic) {
+    if (p == nullptr) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    const int status = enqueue_step(
+        p, x, branch, weight, bias, grad_updated, grad_normalized, updated, normalized, grad_x,
+        grad_branch, grad_parameters, rows, dropout_active, dropout_p, eps, seed, offset,
+        row_base, deterministic);
+    if (status != RLN_OK) {
+        // A step that failed half-way has copies in flight that target the
+        // caller's host buffers; they must not outlive this call.
+        (void)drain(p);
+    }
+    return status;
+}
+
+extern "C" int rln_sm100_host_pipeline_wait(RlnHostPipeline* p) {
+    if (p == nullptr) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    return drain(p);
+}
+
+extern "C" int64_t rln_sm100_host_pipeline_steps_enqueued(const RlnHostPipeline* p) {
+    return p == nullptr ? RLN_ERR_NULL_POINTER : p->steps_enqueued;
+}
+
+extern "C" int rln_sm100_host_pipeline_wait_step(RlnHostPipeline* p, int64_t step) {
+    if (p == nullptr) {
+        return RLN_ERR_NULL_POINTER;
+    }
+    if (step <= 0 || step > p->steps_enqueued) {
+        return RLN_ERR_HOST_BUFFERS;
+    }
+    if (p->steps_enqueued - step >= kStepsTracked) {
+        return RLN_OK;  // its completion entry was reused, which waited for it
+    }
+    const int tracked = static_cast<int>(step % kStepsTracked);
+    RLN_TRY(cudaEventSynchronize(p->step_out[tracked]));
+    RLN_TRY(cudaEventSynchronize(p->step_compute[tracked]));
+    return RLN_OK;
+}
 
 extern "C" int rln_sm100_host_forward_backward(
     RlnHostPipeline* p,
@@ -377,16 +489,6 @@ extern "C" int rln_sm100_host_forward_backward(
         row_base, deterministic);
     // Drain the streams whatever happened: copies that were already enqueued
     // still target the caller's host buffers and must not outlive this call.
-    const cudaError_t drained_in = cudaStreamSynchronize(p->stream_in);
-    const cudaError_t drained_compute = cudaStreamSynchronize(p->stream_compute);
-    const cudaError_t drained_out = cudaStreamSynchronize(p->stream_out);
-    if (status != RLN_OK) {
-        return status;
-    }
-    for (const cudaError_t error : {drained_in, drained_compute, drained_out}) {
-        if (error != cudaSuccess) {
-            return rln::record_cuda_error(error);
-        }
-    }
-    return RLN_OK;
+    const int drained = drain(p);
+    return status != RLN_OK ? status : drained;
 }

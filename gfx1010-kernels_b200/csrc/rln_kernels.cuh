@@ -52,7 +52,7 @@ struct ForwardParams {
     uint32_t threshold;
     uint32_t seed_lo;
     uint32_t seed_hi;
-    uint32_t offset_lo;
+    uint32_t offset_lo;   // Philox block index = word offset / 4 (low, high half)
     uint32_t offset_hi;
     // Philox state kept on the device (set when the launch is recorded into a
     // CUDA graph, so that each replay sees the generator's current state):
@@ -145,8 +145,9 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 counter, uint32_t key0, uin
 // (seed, offset) of this launch: immediate, or read from device memory.
 __device__ __forceinline__ PhiloxState resolve_philox_state(const ForwardParams& p) {
     const uint64_t seed = static_cast<uint64_t>(__ldg(p.device_seed));
+    // word offset -> Philox block index (four words per call), as on the host side
     const uint64_t offset =
-        static_cast<uint64_t>(__ldg(p.device_offset)) + p.device_offset_extra;
+        (static_cast<uint64_t>(__ldg(p.device_offset)) + p.device_offset_extra) >> 2;
     PhiloxState state;
     state.seed_lo = static_cast<uint32_t>(seed);
     state.seed_hi = static_cast<uint32_t>(seed >> 32);
@@ -479,15 +480,14 @@ __device__ __forceinline__ float4 drop_four(float4 b, uint32_t nibble, float sca
 }
 
 // Lane-local pieces of the row arithmetic, shared by the two forward kernels.
-// u = x + dropped, never contracted into an fma with the dropout multiply.
-template <bool kPacked>
+// u = x + dropped, never contracted into an fma with the dropout multiply:
+// always the scalar __fadd_rn.  The two-wide add is NOT safe here -- with a
+// float32 branch nothing stands between the two-wide multiply of the dropout
+// and this add, and the compiler fuses the pair into a two-wide fma, which
+// changes the last bit of `updated` (caught by the float32-branch parity test).
 __device__ __forceinline__ float4 add_residual(float4 x, float4 dropped) {
-    if constexpr (kPacked) {
-        return join4(__fadd2_rn(lo2(x), lo2(dropped)), __fadd2_rn(hi2(x), hi2(dropped)));
-    } else {
-        return make_float4(__fadd_rn(x.x, dropped.x), __fadd_rn(x.y, dropped.y),
-                           __fadd_rn(x.z, dropped.z), __fadd_rn(x.w, dropped.w));
-    }
+    return make_float4(__fadd_rn(x.x, dropped.x), __fadd_rn(x.y, dropped.y),
+                       __fadd_rn(x.z, dropped.z), __fadd_rn(x.w, dropped.w));
 }
 
 // A lane's running sum over its chunks (values, or squares of centred values).
@@ -636,7 +636,7 @@ rln_forward_kernel(const ForwardParams p) {
                 if constexpr (kDropout) {
                     dropped = drop_four<BranchT, kPacked>(dropped, nibble[r][k], p.scale);
                 }
-                const float4 value = add_residual<kPacked>(u[r][k], dropped);
+                const float4 value = add_residual(u[r][k], dropped);
                 u[r][k] = value;
                 const int64_t chunk = row * kChunksPerRow + lane + k * kWarpSize;
                 store_f4<kAligned, kStreamHints>(p.updated, chunk, value);
@@ -765,7 +765,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
             if constexpr (kDropout) {
                 dropped = drop_four<BranchT, kPacked>(dropped, nibble[k], p.scale);
             }
-            const float4 value = add_residual<kPacked>(u[k], dropped);
+            const float4 value = add_residual(u[k], dropped);
             u[k] = value;
             if (valid) {
                 store_f4<kAligned, kStreamHints>(

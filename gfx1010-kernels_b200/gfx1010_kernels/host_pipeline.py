@@ -49,6 +49,15 @@ def _load():
             + [ctypes.c_int64, ctypes.c_int32, ctypes.c_float, ctypes.c_float,
                ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int64, ctypes.c_int32]
         )
+        lib.rln_sm100_host_forward_backward_enqueue.restype = ctypes.c_int
+        lib.rln_sm100_host_forward_backward_enqueue.argtypes = \
+            lib.rln_sm100_host_forward_backward.argtypes
+        lib.rln_sm100_host_pipeline_wait.restype = ctypes.c_int
+        lib.rln_sm100_host_pipeline_wait.argtypes = [_ptr]
+        lib.rln_sm100_host_pipeline_steps_enqueued.restype = ctypes.c_int64
+        lib.rln_sm100_host_pipeline_steps_enqueued.argtypes = [_ptr]
+        lib.rln_sm100_host_pipeline_wait_step.restype = ctypes.c_int
+        lib.rln_sm100_host_pipeline_wait_step.argtypes = [_ptr, ctypes.c_int64]
         _library = lib
     return _library
 
@@ -57,6 +66,32 @@ def _check(status, what):
     if status != 0:
         text = _load().rln_sm100_status_string(status).decode()
         raise RuntimeError(f"{what} failed: {text}")
+
+
+def check_output_tensors(out, shape, hidden, normalized_dtype, branch_dtype):
+    """Raises unless ``out`` is ``(updated, normalized, grad_x, grad_branch,
+    grad_parameters)`` as contiguous HOST tensors of exactly the shapes and types
+    the native call fills.  That call copies ``rows * hidden`` elements straight
+    into the five pointers, so anything else would be written out of bounds."""
+    if not isinstance(out, (tuple, list)) or len(out) != 5:
+        raise RuntimeError(
+            "out must be (updated, normalized, grad_x, grad_branch, grad_parameters)")
+    expected = (
+        ("updated", shape, torch.float32),
+        ("normalized", shape, normalized_dtype),
+        ("grad_x", shape, torch.float32),
+        ("grad_branch", shape, branch_dtype),
+        ("grad_parameters", (2, hidden), torch.float32),
+    )
+    for tensor, (name, wanted_shape, dtype) in zip(out, expected):
+        if not isinstance(tensor, torch.Tensor) or tensor.is_cuda:
+            raise RuntimeError(f"out: {name} must be a host tensor")
+        if tensor.dtype != dtype:
+            raise RuntimeError(f"out: {name} must use {dtype}")
+        if tuple(tensor.shape) != tuple(wanted_shape):
+            raise RuntimeError(f"out: {name} must have shape {tuple(wanted_shape)}")
+        if not tensor.is_contiguous():
+            raise RuntimeError(f"out: {name} must be contiguous")
 
 
 class HostPipeline:
@@ -87,6 +122,7 @@ class HostPipeline:
         self.chunk_rows = int(chunk_rows)
         self.depth = int(depth)
         self._handle = _ptr()
+        self._in_flight = []
         with torch.cuda.device(self.device):
             torch.cuda.current_stream()  # make sure the device's context exists
             status = _load().rln_sm100_host_pipeline_create(
@@ -144,12 +180,21 @@ class HostPipeline:
         row_base=0,
         deterministic=False,
         out=None,
+        wait=True,
     ):
         """One forward + backward over host tensors.
 
         Returns ``(updated, normalized, grad_x, grad_branch, grad_parameters)``
         as host tensors (``out`` is filled and returned when given);
         ``grad_parameters[0]`` is grad_weight and ``[1]`` is grad_bias.
+
+        ``wait=False`` only enqueues the step and returns the (not yet filled)
+        output tensors; ``wait()`` returns once every enqueued step has landed.
+        Steps enqueued back to back overlap -- the next step's first chunks are
+        copied in while this step's last chunks are computed and copied out --
+        which removes the idle chunk at both ends of a lone step.  Until
+        ``wait()`` has returned, do not touch any tensor of an enqueued step
+        (inputs included) and give steps in flight separate ``out`` tensors.
         """
         if self._handle is None:
             raise RuntimeError("the pipeline is closed")
@@ -176,13 +221,18 @@ class HostPipeline:
             raise RuntimeError("empty tensors are unsupported")
         if out is None:
             out = self.allocate_outputs(x.shape)
+        check_output_tensors(out, tuple(x.shape), self.hidden, self.normalized_dtype,
+                             self.branch_dtype)
         updated, normalized, grad_x, grad_branch, grad_parameters = out
-        if normalized.dtype != self.normalized_dtype or grad_branch.dtype != self.branch_dtype:
-            raise RuntimeError("the output tensors do not have the pipeline's dtypes")
         rows = x.numel() // self.hidden
         active = bool(training and dropout_p > 0.0)
+        entry = (_load().rln_sm100_host_forward_backward if wait
+                 else _load().rln_sm100_host_forward_backward_enqueue)
+        if not wait:
+            # keep every tensor of the step alive until a wait has covered it
+            self._in_flight.append((tensors, out))
         with torch.cuda.device(self.device):
-            status = _load().rln_sm100_host_forward_backward(
+            status = entry(
                 self._handle,
                 x.data_ptr(), branch.data_ptr(), weight.data_ptr(), bias.data_ptr(),
                 grad_updated.data_ptr(), grad_normalized.data_ptr(),
@@ -191,5 +241,30 @@ class HostPipeline:
                 rows, int(active), float(dropout_p), float(eps),
                 int(seed), int(offset), int(row_base), int(bool(deterministic)),
             )
+        if status != 0 or wait:
+            # (a failed enqueue has already waited for its copies in flight)
+            self._in_flight.clear()
         _check(status, "rln_sm100_host_forward_backward")
         return out
+
+    def steps_enqueued(self):
+        """How many steps this pipeline has been given so far; right after a
+        ``forward_backward(..., wait=False)`` it is that step's number for
+        ``wait(step=...)``."""
+        if self._handle is None:
+            raise RuntimeError("the pipeline is closed")
+        return int(_load().rln_sm100_host_pipeline_steps_enqueued(self._handle))
+
+    def wait(self, step=None):
+        """Blocks until every step enqueued with ``wait=False`` has landed in its
+        output tensors, or, with ``step=n``, until the n-th step given to this
+        pipeline has (later steps may still be in flight)."""
+        if self._handle is None:
+            raise RuntimeError("the pipeline is closed")
+        with torch.cuda.device(self.device):
+            if step is None:
+                status = _load().rln_sm100_host_pipeline_wait(self._handle)
+                self._in_flight.clear()
+            else:
+                status = _load().rln_sm100_host_pipeline_wait_step(self._handle, int(step))
+        _check(status, "rln_sm100_host_pipeline_wait")

@@ -12,8 +12,11 @@ parameters, same ``state_dict`` keys ``weight`` / ``bias``, loadable from and
 into a plain LayerNorm checkpoint) whose ``forward`` takes the residual stream
 and the branch output and returns ``(updated, normalized)``.  Because weight and
 bias are ordinary parameters reached through autograd, ``DistributedDataParallel``
-all-reduces their gradients with the rest of the model; nothing extra is needed
-for data parallelism.
+buckets their gradients with the rest of the model and all-reduces them in its
+own backward hook; that hook is the data-parallel exchange of this module and
+nothing extra is needed (checked on two gloo ranks against the single-process
+gradients in ``tests/test_modules_ddp_cpu.py``).  Callers that drive the raw
+step themselves use ``gfx1010_kernels.sharded`` instead.
 """
 
 import torch

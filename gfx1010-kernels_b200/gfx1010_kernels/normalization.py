@@ -37,7 +37,10 @@ from ._status import BackendStatus
 MIN_HIDDEN_SIZE = 128
 MAX_HIDDEN_SIZE = 1024
 NATIVE_HIDDEN_SIZES = (128, 256, 384, 512, 768, 1024)
-NATIVE_COMPUTE_CAPABILITY_MAJOR = 10
+# The build emits sm_100a code only, and architecture-specific ("a") targets run
+# on exactly that compute capability: 10.0 (B200), not on other 10.x parts.
+NATIVE_COMPUTE_CAPABILITY = (10, 0)
+NATIVE_COMPUTE_CAPABILITY_MAJOR = NATIVE_COMPUTE_CAPABILITY[0]
 # float16 / float32 are the reference's branch types; bfloat16 is accepted in
 # addition (the sm_100a kernels have it, the gfx1010 ones could not).
 NATIVE_BRANCH_DTYPES = (torch.float16, torch.float32, torch.bfloat16)
@@ -82,7 +85,7 @@ def _native_status(device_index):
     name = torch.cuda.get_device_name(device_index)
     major, minor = torch.cuda.get_device_capability(device_index)
     architecture = f"sm_{major}{minor}"
-    if major != NATIVE_COMPUTE_CAPABILITY_MAJOR:
+    if (major, minor) != NATIVE_COMPUTE_CAPABILITY:
         return BackendStatus(
             False,
             name,

@@ -100,11 +100,17 @@ RLN_API int rln_sm100_last_cuda_error(void);
  *                (layout of :500-511).  Ignored (may be NULL) when
  *                dropout_active == 0.
  *   dropout_active  the caller's (training && dropout_p > 0)
- *   seed, offset Philox4x32-10 key and per-call counter.  Element group
+ *   seed, offset Philox4x32-10 key and per-call position.  `offset` counts
+ *                32-bit words of the generator's stream, as torch's CUDA
+ *                generator does; a Philox call yields four words, so the
+ *                counter holds the block index b = offset / 4 (pass multiples
+ *                of 4: the low two bits are dropped).  Element group
  *                g = ((row_base + row) * hidden + col) / 4 uses counter
- *                (lo32(offset), hi32(offset), lo32(g), hi32(g)), key
+ *                (lo32(b), hi32(b), lo32(g), hi32(g)), key
  *                (lo32(seed), hi32(seed)); output word j decides column 4g+j;
  *                keep <=> word >= (uint32)((double)dropout_p * 2^32)  (:896-899).
+ *                One call uses block b only, so a consumer that starts at
+ *                offset + 4 or later never reuses its words.
  *   row_base     global index of this call's first row.  A row shard that
  *                passes its global offset reproduces the mask of the unsharded
  *                call bit for bit.  0 for an unsharded call.
@@ -137,7 +143,8 @@ RLN_API int rln_sm100_forward(
 
 /*
  * Forward whose Philox (seed, offset) is read from DEVICE memory when the
- * kernel runs: seed = *device_seed, offset = *device_offset + offset_extra.
+ * kernel runs: seed = *device_seed, offset = *device_offset + offset_extra
+ * (in words; the block index is that sum / 4, as in rln_sm100_forward).
  * Everything else as rln_sm100_forward.
  *
  * This is the form a launch recorded into a CUDA graph needs: the reference
@@ -322,6 +329,22 @@ RLN_API int rln_sm100_backward_static_scratch(
  * rln_sm100_host_forward_backward returns after every output has landed in
  * host memory (it synchronises its own streams, nothing else).
  *
+ * rln_sm100_host_forward_backward_enqueue takes the same arguments and returns
+ * as soon as the step is enqueued; rln_sm100_host_pipeline_wait returns once
+ * everything enqueued so far has landed, rln_sm100_host_pipeline_wait_step(p, n)
+ * once the n-th step enqueued on this pipeline has (n counts from 1;
+ * rln_sm100_host_pipeline_steps_enqueued gives the number so far, i.e. the n of
+ * the step just enqueued; an n outside 1..that number is RLN_ERR_HOST_BUFFERS).
+ * At most 8 steps are tracked: enqueueing a ninth first waits for the oldest.
+ * Steps enqueued back to back overlap:
+ * the first chunks of step i+1 are copied in while the last chunks of step i
+ * are computed and copied out, so neither PCIe direction idles between steps
+ * (a lone step leaves each direction idle for one chunk).  Rules for enqueued
+ * steps: every host buffer of a step -- inputs, weight, bias and outputs --
+ * must stay valid and untouched until a wait that covers the step has returned;
+ * steps in flight must not share output buffers; one thread per pipeline.  If _enqueue returns an
+ * error it has already waited for the copies that were in flight.
+ *
  *   x, branch, grad_updated, grad_normalized   host in,  [rows, hidden]
  *   weight, bias                                host in,  float32 [hidden]
  *   updated, normalized, grad_x, grad_branch    host out, [rows, hidden]
@@ -365,6 +388,34 @@ RLN_API int rln_sm100_host_forward_backward(
     uint64_t offset,
     int64_t row_base,
     int32_t deterministic);
+
+RLN_API int rln_sm100_host_forward_backward_enqueue(
+    RlnHostPipeline* pipeline,
+    const float* x,
+    const void* branch,
+    const float* weight,
+    const float* bias,
+    const float* grad_updated,
+    const void* grad_normalized,
+    float* updated,
+    void* normalized,
+    float* grad_x,
+    void* grad_branch,
+    float* grad_parameters,
+    int64_t rows,
+    int32_t dropout_active,
+    float dropout_p,
+    float eps,
+    uint64_t seed,
+    uint64_t offset,
+    int64_t row_base,
+    int32_t deterministic);
+
+RLN_API int rln_sm100_host_pipeline_wait(RlnHostPipeline* pipeline);
+
+RLN_API int64_t rln_sm100_host_pipeline_steps_enqueued(const RlnHostPipeline* pipeline);
+
+RLN_API int rln_sm100_host_pipeline_wait_step(RlnHostPipeline* pipeline, int64_t step);
 
 #ifdef __cplusplus
 }

@@ -21,7 +21,8 @@
  *
  * The dropout bits come from Philox4x32-10 (Salmon et al., SC'11) with the
  * counter layout of the sm_100a kernel: group g = ((row_base + row) * H + col) / 4,
- * counter (lo32(offset), hi32(offset), lo32(g), hi32(g)), key (lo32(seed), hi32(seed)),
+ * block b = offset / 4 (the offset counts 32-bit words, a call yields four),
+ * counter (lo32(b), hi32(b), lo32(g), hi32(g)), key (lo32(seed), hi32(seed)),
  * word j -> column 4g + j, keep <=> word >= threshold.
  */
 #include <math.h>
@@ -85,7 +86,8 @@ void rln_oracle_keep_mask(
     for (int64_t row = 0; row < rows; ++row) {
         for (int32_t col = 0; col < hidden; col += 4) {
             const uint64_t group = ((uint64_t)(row_base + row) * (uint64_t)hidden + (uint64_t)col) / 4;
-            uint32_t counter[4] = {(uint32_t)offset, (uint32_t)(offset >> 32),
+            const uint64_t block = offset >> 2;
+            uint32_t counter[4] = {(uint32_t)block, (uint32_t)(block >> 32),
                                    (uint32_t)group, (uint32_t)(group >> 32)};
             philox4x32_10(counter, (uint32_t)seed, (uint32_t)(seed >> 32));
             for (int j = 0; j < 4; ++j) {

@@ -98,8 +98,10 @@ def dropout_random_words(rows, hidden, seed, offset, row_base=0):
 
     Counter layout of the sm_100a kernel: one Philox call serves the four
     consecutive columns ``4g .. 4g+3`` of element group
-    ``g = ((row_base + row) * hidden + col) / 4``; counter =
-    ``(lo32(offset), hi32(offset), lo32(g), hi32(g))``, key =
+    ``g = ((row_base + row) * hidden + col) / 4``; ``offset`` counts 32-bit
+    words of the generator's stream and a call yields four, so the counter holds
+    the block index ``b = offset // 4``: counter =
+    ``(lo32(b), hi32(b), lo32(g), hi32(g))``, key =
     ``(lo32(seed), hi32(seed))``; output word ``j`` belongs to column
     ``4g + j``.  ``row_base`` is the global index of the first row, so a row
     shard reproduces the mask of the unsharded call.
@@ -111,8 +113,9 @@ def dropout_random_words(rows, hidden, seed, offset, row_base=0):
         + np.arange(groups_per_row, dtype=np.uint64)[None, :]
     )
     counter = np.empty((rows, groups_per_row, 4), dtype=np.uint64)
-    counter[..., 0] = np.uint64(int(offset) & 0xFFFFFFFF)
-    counter[..., 1] = np.uint64((int(offset) >> 32) & 0xFFFFFFFF)
+    block = int(offset) >> 2
+    counter[..., 0] = np.uint64(block & 0xFFFFFFFF)
+    counter[..., 1] = np.uint64((block >> 32) & 0xFFFFFFFF)
     counter[..., 2] = group & _U32
     counter[..., 3] = group >> _SHIFT32
     key = (int(seed) & 0xFFFFFFFF, (int(seed) >> 32) & 0xFFFFFFFF)

@@ -39,6 +39,11 @@ def library():
             _p, _p, _p, _p, _p, _p, _p, _p, _p,
             _i64, _i32, _i32, _i32, _i32, _f32, _f32, _u64, _u64, _i64, _p,
         ]
+        lib.rln_sm100_forward_device_rng.restype = ctypes.c_int
+        lib.rln_sm100_forward_device_rng.argtypes = [
+            _p, _p, _p, _p, _p, _p, _p, _p, _p,
+            _i64, _i32, _i32, _i32, _i32, _f32, _f32, _p, _p, _u64, _i64, _p,
+        ]
         lib.rln_sm100_backward_workspace_bytes.restype = _i64
         lib.rln_sm100_backward_workspace_bytes.argtypes = [_i64, _i32, _i32]
         lib.rln_sm100_backward.restype = ctypes.c_int
@@ -84,6 +89,31 @@ def forward(x, branch, weight, bias, dropout_p, eps, training, seed=0, offset=0,
         _ptr(mask) if active else None,
         rows, hidden, DTYPE_CODES[branch.dtype], DTYPE_CODES[normalized.dtype], int(active),
         dropout_p, eps, seed, offset, row_base, _stream(),
+    )
+    return status, updated, normalized, mean, rstd, mask
+
+
+def forward_device_rng(x, branch, weight, bias, dropout_p, eps, training, device_seed,
+                       device_offset, offset_extra=0, row_base=0,
+                       normalized_dtype=torch.float32):
+    """``rln_sm100_forward_device_rng``: the Philox seed and offset are read by the
+    kernel from two int64 words in device memory (``device_seed``, ``device_offset``:
+    one-element int64 CUDA tensors).  Returns (status, updated, normalized, mean,
+    rstd, mask)."""
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden
+    active = bool(training and dropout_p > 0.0)
+    updated = torch.empty_like(x)
+    normalized = torch.empty(x.shape, dtype=normalized_dtype, device=x.device)
+    mean = torch.empty(rows, device=x.device)
+    rstd = torch.empty(rows, device=x.device)
+    mask = torch.empty(rows * (hidden // 32) if active else 0, dtype=torch.int32, device=x.device)
+    status = library().rln_sm100_forward_device_rng(
+        _ptr(x), _ptr(branch), _ptr(weight), _ptr(bias),
+        _ptr(updated), _ptr(normalized), _ptr(mean), _ptr(rstd),
+        _ptr(mask) if active else None,
+        rows, hidden, DTYPE_CODES[branch.dtype], DTYPE_CODES[normalized.dtype], int(active),
+        dropout_p, eps, _ptr(device_seed), _ptr(device_offset), offset_extra, row_base, _stream(),
     )
     return status, updated, normalized, mean, rstd, mask
 

@@ -35,12 +35,12 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session", autouse=True)
 def built_libraries():
-    """Build the in-tree libraries when they are missing (nvcc cross-compiles
-    without a GPU).  An existing build is used as is."""
+    """Build the in-tree libraries (nvcc cross-compiles without a GPU).  The
+    build is incremental: objects newer than their sources are kept, anything
+    stale is rebuilt, so the tests never run against binaries of older sources."""
     import build as rln_build
 
-    if not (rln_build.KERNEL_LIBRARY.exists() and rln_build.EXTENSION.exists()):
-        rln_build.build_all()
+    rln_build.build_all()
     return rln_build.KERNEL_LIBRARY, rln_build.EXTENSION
 
 

@@ -64,7 +64,10 @@ def test_reference_arm_prints_one_json_line():
     assert record["unit"] == "rows/s" and record["higher_is_better"] is True
     assert record["value"] > 0 and record["n_gpus"] == 1 and record["steps"] == 1
     assert record["config"]["workload"] == "c2_3x1367x128_fp32"
-    assert record["cpu_baseline"]["kind"] == "port" and record["cpu_baseline"]["cores"] >= 1
+    # the reference's own package when oracle/build_ref.py has installed it, else the port
+    installed = (REPO / "oracle" / "_ref" / "gfx1010_kernels" / "normalization.py").exists()
+    assert record["cpu_baseline"]["kind"] == ("reference" if installed else "port")
+    assert record["cpu_baseline"]["cores"] >= 1
     assert record["cpu_baseline"]["value"] == record["value"]
     assert record["e2e"] == {
         "value": record["value"], "unit": "rows/s",
@@ -86,3 +89,25 @@ def test_reference_arm_under_torchrun_prints_on_rank_0_only():
     record = json.loads(lines[0])
     assert record["impl"] == "reference" and record["n_gpus"] == 2
     assert record["config"]["rows_total"] == 2 * 5 * 817
+
+
+def test_cpu_arm_falls_back_to_the_port_without_the_reference_package(bench, monkeypatch, tmp_path):
+    monkeypatch.setattr(bench, "REFERENCE_PACKAGE_DIR", tmp_path)
+    times, threads, kind = bench.time_cpu_reference(64, 128, torch.float16, 0.1, 1, 0)
+    assert kind == "port" and len(times) == 1 and threads >= 1
+
+
+def test_clock_summary_names_the_window_it_used(bench):
+    sampler = bench.ClockSampler(0)
+    sampler.max_mhz = 1965
+    sampler.samples = [(1.0, 1900, 0), (2.0, 1800, 0x4), (3.0, 1700, 0x4), (9.0, 1000, 0x1)]
+    inner = sampler.summary([("timed regions", 1.5, 3.5), ("whole run", 0.0, 10.0)])
+    assert inner["window"] == "timed regions" and inner["samples"] == 2
+    assert inner["sm_mhz"] == 1750 and inner["reasons"] == ["sw_power_cap"]
+    # a span with fewer than two samples is skipped, and the label says which one was used
+    outer = sampler.summary([("timed regions", 2.5, 3.5), ("whole run", 0.0, 10.0)])
+    assert outer["window"] == "whole run" and outer["samples"] == 4
+    nothing = sampler.summary([("timed regions", 20.0, 30.0)])
+    assert nothing["window"] == "all samples of the run" and nothing["samples"] == 4
+    empty = bench.ClockSampler(0)
+    assert empty.summary([("timed regions", 0.0, 1.0)])["window"] == "no samples"

@@ -302,3 +302,31 @@ def test_full_size_16_bit_normalized_is_the_cast_of_the_float32_path(
     torch.cuda.synchronize()
     for a, b in zip(from_narrow[1:], from_wide[1:]):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize(
+    "rows,hidden", [(8 * 1024, 768), (64 * 4096, 1024)], ids=["8x1024x768", "64x4096x1024"]
+)
+def test_parameter_gradients_meet_the_relative_bound_without_the_floor(rows, hidden):
+    """grad_weight / grad_bias against float64 column sums with the bare 1e-4
+    relative bound (no absolute floor), on every column whose exact sum is not a
+    near-total cancellation (|sum| >= 1 % of the sqrt(rows) scale of such sums);
+    both the atomic and the fixed-order path."""
+    x, branch, weight, bias, grad_updated, grad_normalized = device_inputs(
+        rows, hidden, torch.float16, seed=rows % 97
+    )
+    _, updated, _, mean, rstd, mask = cabi.forward(x, branch, weight, bias, 0.1, 1e-5, True)
+    xhat = (updated.double() - mean.double()[:, None]) * rstd.double()[:, None]
+    exact = torch.stack(((grad_normalized.double() * xhat).sum(0), grad_normalized.double().sum(0)))
+    del xhat
+    for deterministic in (False, True):
+        status, _, _, parameters = cabi.backward(
+            grad_updated, grad_normalized, updated, weight, mean, rstd, mask, 0.1, True,
+            torch.float16, deterministic,
+        )
+        assert status == 0
+        relative = (parameters.double() - exact).abs() / exact.abs()
+        meaningful = exact.abs() >= 0.01 * rows ** 0.5
+        assert meaningful.float().mean().item() > 0.95
+        worst = relative[meaningful].max().item()
+        assert worst <= 1e-4, f"worst relative error {worst:.3g} (deterministic={deterministic})"

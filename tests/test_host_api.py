@@ -313,3 +313,36 @@ def test_extension_signatures_keep_the_reference_arity_with_an_optional_tail(bui
     x = torch.randn(2, 128)
     with pytest.raises(RuntimeError, match="x must be a HIP tensor"):
         _C.residual_layer_norm_forward(x, x, x[0], x[0], 0.0, 1e-5, True, 128, 2)
+
+
+def test_host_pipeline_output_tensors_are_checked_before_the_native_call():
+    """Shape, type, layout and residency of caller-supplied result tensors: the
+    native call writes rows * hidden elements into them unchecked."""
+    from gfx1010_kernels.host_pipeline import check_output_tensors
+
+    shape, hidden = (6, 128), 128
+
+    def outputs(**replace):
+        tensors = {
+            "updated": torch.empty(shape), "normalized": torch.empty(shape, dtype=torch.bfloat16),
+            "grad_x": torch.empty(shape), "grad_branch": torch.empty(shape, dtype=torch.float16),
+            "grad_parameters": torch.empty(2, hidden),
+        }
+        tensors.update(replace)
+        return tuple(tensors.values())
+
+    check_output_tensors(outputs(), shape, hidden, torch.bfloat16, torch.float16)
+    cases = {
+        "updated must have shape": outputs(updated=torch.empty(5, 128)),
+        "grad_x must use": outputs(grad_x=torch.empty(shape, dtype=torch.float64)),
+        "normalized must use": outputs(normalized=torch.empty(shape)),
+        "grad_branch must be contiguous": outputs(
+            grad_branch=torch.empty(128, 6, dtype=torch.float16).t()),
+        "grad_parameters must have shape": outputs(grad_parameters=torch.empty(2 * hidden)),
+        "updated must be a host tensor": outputs(updated=None),
+    }
+    for message, out in cases.items():
+        with pytest.raises(RuntimeError, match=message):
+            check_output_tensors(out, shape, hidden, torch.bfloat16, torch.float16)
+    with pytest.raises(RuntimeError, match="out must be"):
+        check_output_tensors(outputs()[:4], shape, hidden, torch.bfloat16, torch.float16)

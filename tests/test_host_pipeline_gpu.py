@@ -97,3 +97,55 @@ def test_host_pipeline_rejects_bad_arguments():
             pipeline.forward_backward(x.cuda(), x.half(), torch.ones(128), torch.zeros(128), x, x)
         with pytest.raises(RuntimeError, match=r"dropout_p must be in \[0, 1\)"):
             pipeline.forward_backward(x, x.half(), torch.ones(128), torch.zeros(128), x, x, 1.0)
+        short = list(pipeline.allocate_outputs((4, 128)))
+        short[2] = torch.empty(3, 128)
+        with pytest.raises(RuntimeError, match="grad_x must have shape"):
+            pipeline.forward_backward(
+                x, x.half(), torch.ones(128), torch.zeros(128), x, x, out=tuple(short))
+
+
+@pytest.mark.parametrize("depth", [2, 3])
+def test_enqueued_steps_overlap_and_match_synchronous_calls(depth):
+    """Four steps enqueued back to back (different Philox offsets, two sets of
+    inputs, separate output tensors, chunk counts that do not divide the slot
+    ring evenly) against the same four steps run one at a time, in deterministic
+    mode: every output bit for bit."""
+    rows, hidden, chunk_rows = 1100, 256, 256          # 5 chunks per step
+    first = [t.pin_memory() for t in draw_inputs((rows,), hidden, torch.float16, 3, device="cpu")]
+    second = [t.pin_memory() for t in draw_inputs((rows,), hidden, torch.float16, 4, device="cpu")]
+    steps = [(first, 0), (second, 4), (first, 8), (second, 12)]
+    with HostPipeline(hidden, torch.float16, chunk_rows=chunk_rows, depth=depth) as pipeline:
+        expected = [
+            [t.clone() for t in pipeline.forward_backward(
+                *inputs, 0.1, 1e-5, True, seed=9, offset=offset, row_base=70, deterministic=True)]
+            for inputs, offset in steps
+        ]
+        outputs = [pipeline.allocate_outputs((rows, hidden)) for _ in steps]
+        for out in outputs:
+            for tensor in out:
+                tensor.fill_(float("nan"))
+        already = pipeline.steps_enqueued()
+        for (inputs, offset), out in zip(steps, outputs):
+            returned = pipeline.forward_backward(
+                *inputs, 0.1, 1e-5, True, seed=9, offset=offset, row_base=70,
+                deterministic=True, out=out, wait=False,
+            )
+            assert returned is out
+        assert pipeline.steps_enqueued() == already + len(steps)
+        # the first enqueued step alone: its outputs are complete after this wait
+        pipeline.wait(step=already + 1)
+        for a, b in zip(outputs[0], expected[0]):
+            assert torch.equal(a, b)
+        with pytest.raises(RuntimeError, match="host-buffer pipeline"):
+            pipeline.wait(step=already + len(steps) + 1)
+        pipeline.wait()
+        pipeline.wait()      # nothing left: returns at once
+        # a synchronous call after enqueued ones still works
+        after = pipeline.forward_backward(
+            *first, 0.1, 1e-5, True, seed=9, offset=0, row_base=70, deterministic=True)
+    for got, want in zip(outputs, expected):
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+    for a, b in zip(after, expected[0]):
+        assert torch.equal(a, b)
+    assert not torch.equal(expected[0][0], expected[2][0])   # the offsets matter

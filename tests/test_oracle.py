@@ -59,6 +59,24 @@ def test_keep_mask_is_shard_invariant_and_offset_sensitive():
     assert big.shape == (1, 128)
 
 
+def test_offset_counts_words_and_one_call_uses_one_philox_block():
+    """The offset is in 32-bit words (torch's generator convention); a Philox call
+    yields four, so the counter holds offset // 4: offsets inside one block give
+    the same words, the next block gives others, and the words of element group
+    g at offset o are exactly Philox(counter = (o // 4, g), key = seed) -- the
+    block a later consumer starting at o + 4 can never produce again."""
+    rows, hidden, seed = 3, 128, 77
+    base = rln_oracle.dropout_random_words(rows, hidden, seed, 8)
+    assert np.array_equal(base, rln_oracle.dropout_random_words(rows, hidden, seed, 11))
+    assert not np.array_equal(base, rln_oracle.dropout_random_words(rows, hidden, seed, 12))
+    big = (1 << 35) + 40
+    words = rln_oracle.dropout_random_words(rows, hidden, seed, big, row_base=5)
+    group = 5 * (hidden // 4) + 7                      # row 0, columns 28..31
+    counter = np.array([[(big >> 2) & 0xFFFFFFFF, (big >> 2) >> 32, group, 0]], dtype=np.uint64)
+    expected = rln_oracle.philox4x32_10(counter, (seed, 0)).reshape(-1)
+    assert np.array_equal(words[0, 28:32], expected.astype(words.dtype))
+
+
 def test_kept_fraction_is_within_four_sigma():
     p = 0.1
     keep = rln_oracle.dropout_keep(512, 768, p, seed=0, offset=0)

@@ -332,6 +332,43 @@ def test_deterministic_replay_is_bitwise_and_close_to_atomic_path():
     assert torch.equal(first[1], atomic[1]) and torch.equal(first[2], atomic[2])
 
 
+@pytest.mark.parametrize("hidden", [128, 256, 768, 1024])
+@pytest.mark.parametrize("seed,offset,extra", [(0, 0, 0), (1234, 8, 4), (2 ** 40 + 5, 2 ** 33, 12)])
+def test_device_resident_philox_state_gives_the_oracle_mask(hidden, seed, offset, extra):
+    """The kernels that read (seed, offset) from device memory -- the ones a CUDA
+    graph records -- checked directly against the Philox oracle for
+    (seed, offset + offset_extra), and bit for bit against the immediate-state
+    kernels on every output.  No graph is involved: the two words are plain
+    int64 device tensors."""
+    rows, p = 301, 0.1
+    x, branch, weight, bias, _, _ = draw_inputs((rows,), hidden, torch.float16, 41)
+    device_seed = torch.tensor([seed], dtype=torch.int64, device="cuda")
+    device_offset = torch.tensor([offset], dtype=torch.int64, device="cuda")
+    from_device = cabi.forward_device_rng(
+        x, branch, weight, bias, p, 1e-5, True, device_seed, device_offset, offset_extra=extra,
+        row_base=17,
+    )
+    immediate = cabi.forward(x, branch, weight, bias, p, 1e-5, True, seed=seed,
+                             offset=offset + extra, row_base=17)
+    torch.cuda.synchronize()
+    assert from_device[0] == 0 and immediate[0] == 0, cabi.status_text(from_device[0])
+    keep = unpack_mask_device(from_device[5], rows, hidden)
+    expected = oracle_keep(rows, hidden, p, seed, offset + extra, row_base=17)
+    assert torch.equal(keep, expected), "device-state mask differs from the Philox oracle"
+    for a, b in zip(from_device[1:], immediate[1:]):
+        assert torch.equal(a, b)
+    # the state is read at run time: changing the words changes the next launch
+    device_offset.add_(4)
+    moved = cabi.forward_device_rng(
+        x, branch, weight, bias, p, 1e-5, True, device_seed, device_offset, offset_extra=extra,
+        row_base=17,
+    )
+    assert torch.equal(
+        unpack_mask_device(moved[5], rows, hidden),
+        oracle_keep(rows, hidden, p, seed, offset + extra + 4, row_base=17),
+    )
+
+
 def test_parameter_gradients_can_be_skipped():
     x, branch, weight, bias, grad_updated, grad_normalized = draw_inputs(
         (19,), 256, torch.float16, 9
