@@ -579,11 +579,14 @@ def sharded_check(runner, rank, world, rows_total, offset):
         training=True, seed=0, offset=offset,
     )
     reduced = torch.stack((result.grad_weight, result.grad_bias)).double()
-    floor = 1e-5 * float(rows_total) ** 0.5
-    excess = (reduced - expected).abs() - (1e-4 * expected.abs() + floor)
-    gradients_ok = bool((excess <= 0).all().item())
-    worst_relative = float(
-        ((reduced - expected).abs() / expected.abs().clamp_min(floor)).max().item())
+    scale = float(rows_total) ** 0.5      # typical size of a column sum
+    floor = 1e-5 * scale
+    difference = (reduced - expected).abs()
+    tolerance_used = float((difference / (1e-4 * expected.abs() + floor)).max().item())
+    gradients_ok = tolerance_used <= 1.0
+    # bare relative error on the columns that are not near-total cancellations
+    meaningful = expected.abs() >= 0.01 * scale
+    worst_relative = float((difference / expected.abs())[meaningful].max().item())
     row_local_ok = all(
         torch.equal(a, b) for a, b in (
             (result.updated, updated), (result.normalized, normalized), (result.grad_x, grad_x),
@@ -619,16 +622,17 @@ def sharded_check(runner, rank, world, rows_total, offset):
             del zeros, whole
     else:
         masks_ok = False
-    flags = torch.tensor([gradients_ok, row_local_ok, masks_ok, worst_relative], device=device,
-                         dtype=torch.float64)
+    flags = torch.tensor([gradients_ok, row_local_ok, masks_ok, worst_relative, tolerance_used],
+                         device=device, dtype=torch.float64)
     worst = flags.clone()
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
     record = {
         "ok": bool(flags[0] > 0 and flags[1] > 0 and flags[2] > 0),
         "all_reduced_equals_fp64_sum_of_rank_buffers": bool(flags[0] > 0),
-        "worst_relative_error": float(worst[3]),
         "tolerance": "1e-4 relative + 1e-5*sqrt(rows_total) absolute",
+        "worst_fraction_of_tolerance": float(worst[4]),
+        "worst_relative_error_where_sum_exceeds_1pct_of_sqrt_rows": float(worst[3]),
         "row_local_outputs_bit_identical_to_raw_calls": bool(flags[1] > 0),
         "rank_masks_equal_unsharded_mask": bool(flags[2] > 0),
         "mask_rows_compared_per_rank": 2 * window,
@@ -845,7 +849,7 @@ def run_native_arm(args, rank, local_rank, world):
     has_public = public_ms is not None
     stats = [forward_ms, backward_ms, public_ms or 0.0]
     if e2e is not None:
-        stats += [e2e["ms"], e2e["public_ms"], e2e["copy_ms"]]
+        stats += [e2e["ms"], e2e["public_ms"], e2e["copy_ms"], e2e["chunked_copy_ms"]]
     stats = max_over_ranks(stats, device, world)
     forward_ms, backward_ms, public_ms = stats[:3]
 
@@ -927,7 +931,7 @@ def run_native_arm(args, rank, local_rank, world):
             "clocks": clocks,
         }
         if e2e is not None:
-            e2e_ms, e2e_public_ms, copy_ms = stats[3:6]
+            e2e_ms, e2e_public_ms, copy_ms, chunked_copy_ms = stats[3:7]
             line["e2e"] = {
                 "value": total_rows * e2e["steps"] / (e2e_ms * 1e-3),
                 "unit": UNIT,
@@ -951,6 +955,14 @@ def run_native_arm(args, rank, local_rank, world):
             }
             line["e2e"]["fraction_of_copy_ceiling"] = (
                 line["e2e"]["value"] / line["e2e"]["copy_ceiling_value"])
+            line["e2e"]["chunked_copy_ceiling_value"] = (
+                total_rows * e2e["steps"] / (chunked_copy_ms * 1e-3))
+            line["e2e"]["chunked_copy_ceiling_path"] = (
+                "the same bytes in the pipeline's own pattern (8,192-row chunks, four copies "
+                "in and four out per chunk, two streams), no kernels, no dependencies: what "
+                "chunked bidirectional copies reach on this box")
+            line["e2e"]["fraction_of_chunked_copy_ceiling"] = (
+                line["e2e"]["value"] / line["e2e"]["chunked_copy_ceiling_value"])
         print(json.dumps(line), flush=True)
         checks = [check] + ([strong.get("sharded_check")] if strong else [])
         failed = any(entry is not None and not entry["ok"] for entry in checks)
@@ -1080,13 +1092,26 @@ def run_end_to_end(args, device, host, weight, bias, dropout_p, world, residual_
             for target, source in zip(outputs[:4], device_outputs):
                 target.copy_(source, non_blocking=True)
 
-    steps = max(2, min(args.steps, 5))
+    def chunked_copy_step():
+        # the pipeline's own copy pattern -- per 8,192-row chunk four copies in, four
+        # out -- with no kernels and no dependency between the two directions
+        for begin in range(0, rows, pipeline.chunk_rows):
+            end = min(rows, begin + pipeline.chunk_rows)
+            with torch.cuda.stream(in_stream):
+                for target, source in zip(device_inputs, host_inputs):
+                    target[begin:end].copy_(source[begin:end], non_blocking=True)
+            with torch.cuda.stream(out_stream):
+                for target, source in zip(outputs[:4], device_outputs):
+                    target[begin:end].copy_(source[begin:end], non_blocking=True)
+
+    steps = max(2, min(args.steps, 6))
     pipeline_ms = timed(pipeline_step, steps)
     public_ms = timed(public_api_step, steps)
     copy_ms = timed(copy_step, steps)
+    chunked_copy_ms = timed(chunked_copy_step, steps)
     pipeline.close()
-    return {"ms": pipeline_ms, "public_ms": public_ms, "copy_ms": copy_ms, "steps": steps,
-            "h2d": h2d, "d2h": d2h}
+    return {"ms": pipeline_ms, "public_ms": public_ms, "copy_ms": copy_ms,
+            "chunked_copy_ms": chunked_copy_ms, "steps": steps, "h2d": h2d, "d2h": d2h}
 
 
 def main(argv=None):

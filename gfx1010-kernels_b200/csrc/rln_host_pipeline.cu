@@ -62,9 +62,12 @@ struct RlnHostPipeline {
     cudaStream_t stream_in = nullptr;
     cudaStream_t stream_compute = nullptr;
     cudaStream_t stream_out = nullptr;
-    float* weight = nullptr;
-    float* bias = nullptr;
-    float* total = nullptr;
+    // Two sets, alternating from step to step: a step enqueued behind another
+    // one copies its parameters in, and resets its gradient sums, while the
+    // previous step's last kernels and last copy-out still use theirs.
+    float* weight[2] = {nullptr, nullptr};
+    float* bias[2] = {nullptr, nullptr};
+    float* total[2] = {nullptr, nullptr};
     int64_t chunks_enqueued = 0;  // position in the slot ring; runs on across calls
     // Completion of the most recent steps: step n (1-based count of enqueued
     // steps) has landed once both events of entry n % kStepsTracked fired.
@@ -103,9 +106,11 @@ void release(RlnHostPipeline* p) {
         if (p->step_out[n]) cudaEventDestroy(p->step_out[n]);
         if (p->step_compute[n]) cudaEventDestroy(p->step_compute[n]);
     }
-    cudaFree(p->weight);
-    cudaFree(p->bias);
-    cudaFree(p->total);
+    for (int set = 0; set < 2; ++set) {
+        cudaFree(p->weight[set]);
+        cudaFree(p->bias[set]);
+        cudaFree(p->total[set]);
+    }
     if (p->stream_in) cudaStreamDestroy(p->stream_in);
     if (p->stream_compute) cudaStreamDestroy(p->stream_compute);
     if (p->stream_out) cudaStreamDestroy(p->stream_out);
@@ -130,9 +135,11 @@ cudaError_t allocate(RlnHostPipeline* p) {
     RLN_TRY(cudaStreamCreateWithFlags(&p->stream_in, cudaStreamNonBlocking));
     RLN_TRY(cudaStreamCreateWithFlags(&p->stream_compute, cudaStreamNonBlocking));
     RLN_TRY(cudaStreamCreateWithFlags(&p->stream_out, cudaStreamNonBlocking));
-    RLN_TRY(cudaMalloc(&p->weight, p->hidden * sizeof(float)));
-    RLN_TRY(cudaMalloc(&p->bias, p->hidden * sizeof(float)));
-    RLN_TRY(cudaMalloc(&p->total, 2 * p->hidden * sizeof(float)));
+    for (int set = 0; set < 2; ++set) {
+        RLN_TRY(cudaMalloc(&p->weight[set], p->hidden * sizeof(float)));
+        RLN_TRY(cudaMalloc(&p->bias[set], p->hidden * sizeof(float)));
+        RLN_TRY(cudaMalloc(&p->total[set], 2 * p->hidden * sizeof(float)));
+    }
     for (int n = 0; n < kStepsTracked; ++n) {
         RLN_TRY(cudaEventCreateWithFlags(&p->step_out[n], cudaEventDisableTiming));
         RLN_TRY(cudaEventCreateWithFlags(&p->step_compute[n], cudaEventDisableTiming));
@@ -259,7 +266,8 @@ int enqueue_step(
     uint64_t seed,
     uint64_t offset,
     int64_t row_base,
-    int32_t deterministic) {
+    int32_t deterministic,
+    bool streaming) {
     if (p == nullptr || x == nullptr || branch == nullptr || weight == nullptr || bias == nullptr
         || grad_updated == nullptr || grad_normalized == nullptr || updated == nullptr
         || normalized == nullptr || grad_x == nullptr || grad_branch == nullptr
@@ -291,26 +299,44 @@ int enqueue_step(
     // The slot ring and its events carry over from the previous call: a step
     // enqueued behind another one (rln_sm100_host_forward_backward_enqueue) reuses
     // a slot only after that slot's kernels ran and its results left.
-    const int tracked = static_cast<int>((p->steps_enqueued + 1) % kStepsTracked);
+    const int64_t step = p->steps_enqueued + 1;
+    const int tracked = static_cast<int>(step % kStepsTracked);
     if (p->steps_enqueued >= kStepsTracked) {
         // the completion entry is reused: the step that held it must have landed
         RLN_TRY(cudaEventSynchronize(p->step_out[tracked]));
         RLN_TRY(cudaEventSynchronize(p->step_compute[tracked]));
     }
+    // Every copy goes through one of the two copy streams and the compute
+    // stream holds kernels only.  (A small copy on the compute stream queues
+    // behind whatever the copy engine of its direction already holds -- the
+    // previous step's last chunks -- and would stall the kernels behind it
+    // until then, which serialises consecutive steps.)
+    const int set = static_cast<int>(step & 1);
+    float* const device_weight = p->weight[set];
+    float* const device_bias = p->bias[set];
+    float* const device_total = p->total[set];
+    if (step > 2) {
+        // this set was used by step - 2: its kernels must be done before the
+        // parameters are overwritten, its sums copied out before they are reset
+        const int before = static_cast<int>((step - 2) % kStepsTracked);
+        RLN_TRY(cudaStreamWaitEvent(p->stream_in, p->step_compute[before], 0));
+        RLN_TRY(cudaStreamWaitEvent(p->stream_compute, p->step_out[before], 0));
+    }
     RLN_TRY(cudaMemcpyAsync(
-        p->weight, weight, hidden * sizeof(float), cudaMemcpyHostToDevice, p->stream_compute));
+        device_weight, weight, hidden * sizeof(float), cudaMemcpyHostToDevice, p->stream_in));
     RLN_TRY(cudaMemcpyAsync(
-        p->bias, bias, hidden * sizeof(float), cudaMemcpyHostToDevice, p->stream_compute));
+        device_bias, bias, hidden * sizeof(float), cudaMemcpyHostToDevice, p->stream_in));
+    // (the kernels of the first chunk wait for that chunk's in_ready event, which
+    // the copy-in stream records after these two copies)
 
-    int64_t chunk_index = 0;
-    for (int64_t begin = 0; begin < rows; begin += p->chunk_rows, ++chunk_index) {
+    // Copy-in of the chunk that starts at row `begin` into the next slot of the ring.
+    auto enqueue_copy_in = [&](int64_t begin, Slot** taken) -> int {
         const int64_t count = rows - begin < p->chunk_rows ? rows - begin : p->chunk_rows;
         const size_t elements = static_cast<size_t>(count) * hidden;
         const size_t first = static_cast<size_t>(begin) * hidden;
         Slot& slot = p->slots[p->chunks_enqueued % p->depth];
         ++p->chunks_enqueued;
-
-        // copy in (the slot's inputs are free once its previous kernels ran)
+        // the slot's inputs are free once its previous kernels ran
         if (slot.used) {
             RLN_TRY(cudaStreamWaitEvent(p->stream_in, slot.computed, 0));
         }
@@ -326,6 +352,41 @@ int enqueue_step(
             slot.grad_normalized, grad_normalized_bytes + first * normalized_element,
             elements * normalized_element, cudaMemcpyHostToDevice, p->stream_in));
         RLN_TRY(cudaEventRecord(slot.in_ready, p->stream_in));
+        *taken = &slot;
+        return RLN_OK;
+    };
+
+    // The copy-in runs one chunk ahead of the loop below.  For steps that stream
+    // one behind the other (`streaming`, the enqueue entry) the copy-out of a
+    // chunk additionally waits until the NEXT chunk has arrived.  Both PCIe
+    // directions move a chunk in about the same time, so without that rule they
+    // fall into lockstep: chunk c+1 arrives just as chunk c has left, and the
+    // copy-out engine then idles for the kernels of chunk c+1 plus two
+    // cross-stream hand-overs before it has anything to send, once per chunk.
+    // With the rule the kernels of chunk c+1 run while chunk c leaves (measured
+    // on streamed steps of 87,381 x 768: -2 % with 8,192-row chunks, -6 % with
+    // 2,048-row chunks).  A lone step does not get the rule: it would start its
+    // copy-out one chunk later and finish later (+4 % with 8,192-row chunks).
+    Slot* current = nullptr;
+    {
+        const int status = enqueue_copy_in(0, &current);
+        if (status != RLN_OK) {
+            return status;
+        }
+    }
+    int64_t chunk_index = 0;
+    for (int64_t begin = 0; begin < rows; begin += p->chunk_rows, ++chunk_index) {
+        const int64_t count = rows - begin < p->chunk_rows ? rows - begin : p->chunk_rows;
+        const size_t elements = static_cast<size_t>(count) * hidden;
+        const size_t first = static_cast<size_t>(begin) * hidden;
+        Slot* next = nullptr;
+        if (begin + p->chunk_rows < rows) {
+            const int status = enqueue_copy_in(begin + p->chunk_rows, &next);
+            if (status != RLN_OK) {
+                return status;
+            }
+        }
+        Slot& slot = *current;
 
         // compute (the slot's outputs are free once its previous results left)
         RLN_TRY(cudaStreamWaitEvent(p->stream_compute, slot.in_ready, 0));
@@ -333,14 +394,15 @@ int enqueue_step(
             RLN_TRY(cudaStreamWaitEvent(p->stream_compute, slot.drained, 0));
         }
         int status = rln_sm100_forward(
-            slot.x, slot.branch, p->weight, p->bias, slot.updated, slot.normalized, slot.mean,
-            slot.rstd, slot.mask, count, p->hidden, p->branch_dtype, p->normalized_dtype,
-            dropout_active, dropout_p, eps, seed, offset, row_base + begin, p->stream_compute);
+            slot.x, slot.branch, device_weight, device_bias, slot.updated, slot.normalized,
+            slot.mean, slot.rstd, slot.mask, count, p->hidden, p->branch_dtype,
+            p->normalized_dtype, dropout_active, dropout_p, eps, seed, offset, row_base + begin,
+            p->stream_compute);
         if (status != RLN_OK) {
             return status;
         }
         status = rln_sm100_backward(
-            slot.grad_updated, slot.grad_normalized, slot.updated, p->weight, slot.mean,
+            slot.grad_updated, slot.grad_normalized, slot.updated, device_weight, slot.mean,
             slot.rstd, slot.mask, slot.grad_x, slot.grad_branch, slot.grad_parameters,
             slot.workspace, p->workspace_bytes, count, p->hidden, p->branch_dtype,
             p->normalized_dtype, dropout_active, dropout_p, deterministic, p->stream_compute);
@@ -349,12 +411,15 @@ int enqueue_step(
         }
         const int parameter_count = static_cast<int>(2 * hidden);
         accumulate_parameters_kernel<<<(parameter_count + 255) / 256, 256, 0, p->stream_compute>>>(
-            p->total, slot.grad_parameters, parameter_count, chunk_index == 0 ? 1 : 0);
+            device_total, slot.grad_parameters, parameter_count, chunk_index == 0 ? 1 : 0);
         RLN_TRY(cudaGetLastError());
         RLN_TRY(cudaEventRecord(slot.computed, p->stream_compute));
 
         // copy out
         RLN_TRY(cudaStreamWaitEvent(p->stream_out, slot.computed, 0));
+        if (streaming && next != nullptr) {
+            RLN_TRY(cudaStreamWaitEvent(p->stream_out, next->in_ready, 0));
+        }
         RLN_TRY(cudaMemcpyAsync(
             updated + first, slot.updated, elements * 4, cudaMemcpyDeviceToHost, p->stream_out));
         RLN_TRY(cudaMemcpyAsync(
@@ -367,12 +432,15 @@ int enqueue_step(
             elements * branch_element, cudaMemcpyDeviceToHost, p->stream_out));
         RLN_TRY(cudaEventRecord(slot.drained, p->stream_out));
         slot.used = true;
+        current = next;
     }
-    RLN_TRY(cudaMemcpyAsync(
-        grad_parameters, p->total, 2 * hidden * sizeof(float), cudaMemcpyDeviceToHost,
-        p->stream_compute));
-    RLN_TRY(cudaEventRecord(p->step_out[tracked], p->stream_out));
+    // the sums leave on the copy-out stream, behind the last chunk's results
     RLN_TRY(cudaEventRecord(p->step_compute[tracked], p->stream_compute));
+    RLN_TRY(cudaStreamWaitEvent(p->stream_out, p->step_compute[tracked], 0));
+    RLN_TRY(cudaMemcpyAsync(
+        grad_parameters, device_total, 2 * hidden * sizeof(float), cudaMemcpyDeviceToHost,
+        p->stream_out));
+    RLN_TRY(cudaEventRecord(p->step_out[tracked], p->stream_out));
     ++p->steps_enqueued;
     return RLN_OK;
 }
@@ -423,7 +491,7 @@ extern "C" int rln_sm100_host_forward_backward_enqueue(
     const int status = enqueue_step(
         p, x, branch, weight, bias, grad_updated, grad_normalized, updated, normalized, grad_x,
         grad_branch, grad_parameters, rows, dropout_active, dropout_p, eps, seed, offset,
-        row_base, deterministic);
+        row_base, deterministic, /*streaming=*/true);
     if (status != RLN_OK) {
         // A step that failed half-way has copies in flight that target the
         // caller's host buffers; they must not outlive this call.
@@ -486,7 +554,7 @@ extern "C" int rln_sm100_host_forward_backward(
     const int status = enqueue_step(
         p, x, branch, weight, bias, grad_updated, grad_normalized, updated, normalized, grad_x,
         grad_branch, grad_parameters, rows, dropout_active, dropout_p, eps, seed, offset,
-        row_base, deterministic);
+        row_base, deterministic, /*streaming=*/false);
     // Drain the streams whatever happened: copies that were already enqueued
     // still target the caller's host buffers and must not outlive this call.
     const int drained = drain(p);
