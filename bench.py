@@ -87,7 +87,7 @@ def workload(name):
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE backward launch,
 # taken from an ncu capture of that workload (two launches, --set full), per workload.
 NCU_BACKWARD_TRAFFIC_BYTES = {
-    "h768_64Mi": 814_518_016 + 363_732_992,
+    "h768_64Mi": 814_516_480 + 364_516_352,
     "h768_64Mi_bf16_normalized": 680_267_008 + 363_772_160,
 }
 # the extension's element type codes (False/0 float32, True/1 float16, 2 bfloat16)

@@ -14,7 +14,9 @@ asked of the sm_100a kernels through the same raw ``_C`` entry points:
                and with the fixed-order path of
                ``torch.use_deterministic_algorithms(True)`` (partials + second
                kernel): what grad_weight / grad_bias cost on top of the
-               row-local gradients.
+               row-local gradients.  In deterministic mode torch also fills
+               every fresh output tensor with NaN before the kernels run;
+               ``--disable-deterministic-fill`` takes that out of the figure.
 
 Before any timing the scalar and deterministic results are compared with the
 vectorised / atomic ones (bit-identical row-local outputs, parameter sums
@@ -185,7 +187,14 @@ def main(argv=None):
     parser.add_argument("--warmup", type=int, default=50)
     parser.add_argument("--reps", type=int, default=200)
     parser.add_argument("--rounds", type=int, default=3)
+    parser.add_argument(
+        "--disable-deterministic-fill", action="store_true",
+        help="switch off torch.utils.deterministic.fill_uninitialized_memory: in deterministic "
+             "mode torch fills every freshly allocated output with NaN, which the 'deterministic' "
+             "column otherwise includes (the reference's benchmark has the same switch)")
     args = parser.parse_args(argv)
+    if args.disable_deterministic_fill:
+        torch.utils.deterministic.fill_uninitialized_memory = False
     if not torch.cuda.is_available():
         raise SystemExit("this benchmark needs a CUDA device")
     runners = {"forward": run_forward, "backward": run_backward, "parameters": run_parameters}
