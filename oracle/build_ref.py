@@ -15,6 +15,8 @@ process of its own and time the reference's public call.
 
     python oracle/build_ref.py [--reference /path/to/gfx1010-kernels]
 
+(default: ``$RLN_REFERENCE``, else a directory ``reference`` beside this repository).
+
 Without a reference checkout nothing is written and ``bench.py`` falls back to
 the restatement in ``oracle/rln_oracle.py`` (``cpu_baseline.kind`` "port").
 """
@@ -24,6 +26,7 @@ from __future__ import annotations
 import argparse
 import hashlib
 import json
+import os
 import shutil
 import sys
 from pathlib import Path
@@ -31,7 +34,9 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 TARGET = HERE / "_ref"
 PACKAGE = "gfx1010_kernels"
-DEFAULT_REFERENCE = Path("/root/reference")
+# a checkout of the reference project: $RLN_REFERENCE, else a directory named
+# "reference" next to this repository
+DEFAULT_REFERENCE = Path(os.environ.get("RLN_REFERENCE") or HERE.parent.parent / "reference")
 
 
 def build(reference: Path = DEFAULT_REFERENCE):
