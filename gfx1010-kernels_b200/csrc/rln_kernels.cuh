@@ -412,16 +412,17 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // ---------------------------------------------------------------------------
-// Two optional forms of the arithmetic core.  Both are template parameters of
-// the kernels (the variant benchmark times every combination; the launch tables
-// in rln_launch.h say what ships).
+// Two optional forms of the arithmetic core, a template parameter of the
+// kernels and a macro (the variant benchmark times the combinations; the launch
+// tables in rln_launch.h say what ships).
 //   kPacked     two-wide fp32 instructions (add/mul/fma .f32x2 of sm_100) on
 //               the (x, y) and (z, w) halves of a chunk.  Every lane-local
-//               operation keeps its rounding (round-to-nearest, no flush), so
-//               `updated` and the affine output are the bits of the scalar
-//               form; only the association of the per-lane partial sums
-//               differs.  Pays where the forward runs at 32 warps per SM on a
-//               64-register budget (H = 384: +6 %); neutral or slower elsewhere.
+//               operation keeps its rounding (round-to-nearest, no flush) and
+//               the residual add stays scalar (see add_residual), so `updated`
+//               and the affine output are the bits of the scalar form; only
+//               the association of the per-lane partial sums differs.  Pays
+//               where the forward runs at 32 warps per SM on a 64-register
+//               budget (H = 384: +5 %); neutral or slower elsewhere.
 //   RLN_FWD_MASK_REDUX (macro, 0)  the eight lanes of a mask word combine their
 //               nibbles with one redux.sync.or over the lane group instead of
 //               three shuffle + or steps.  Measured 25 % slower for the forward

@@ -280,3 +280,33 @@ def test_async_steps_chained_through_previous_give_the_synchronous_sums(tmp_path
     mp.spawn(worker_async_chain, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
     for rank in range(2):
         assert (tmp_path / f"rank{rank}.txt").read_text() == "True True"
+
+
+def worker_local_sums(rank, world, port, out_dir):
+    """all_reduce=False: a rank that works alone while a process group exists
+    (gradient accumulation) issues no collective -- rank 1 does not call at all,
+    so a collective here would time out -- and keeps its own sums."""
+    init(rank, world, port, timeout=10)
+    try:
+        outcome = "idle"
+        if rank == 0:
+            x, branch, weight, bias, grad_updated, grad_normalized = global_problem()
+            result = sharded_forward_backward(
+                x, branch, weight, bias, grad_updated, grad_normalized,
+                row_base=0, dropout_p=P, eps=EPS, seed=SEED, offset=OFFSET,
+                compute=oracle_compute, all_reduce=False,
+            )
+            whole = oracle_compute(x, branch, weight, bias, grad_updated, grad_normalized,
+                                   P, EPS, True, SEED, OFFSET, 0)
+            outcome = str(torch.equal(result.grad_weight, whole[4][0])
+                          and torch.equal(result.grad_bias, whole[4][1]))
+        (Path(out_dir) / f"rank{rank}.txt").write_text(outcome)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_all_reduce_can_be_skipped_for_local_accumulation(tmp_path):
+    mp.spawn(worker_local_sums, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "rank0.txt").read_text() == "True"
+    assert (tmp_path / "rank1.txt").read_text() == "idle"

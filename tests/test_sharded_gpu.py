@@ -84,6 +84,13 @@ def _nccl_worker(rank, world, port, out_dir):
             )
             handles.append(pending)
         results = [handle.wait() for handle in handles]
+        # a second NCCL group made by the module's helper gives the same sums
+        group = sharded.new_high_priority_group()
+        regrouped = sharded_forward_backward(
+            *shard, row_base=begin, dropout_p=p, seed=seed, offset=8, group=group)
+        assert torch.equal(regrouped.mask, results[2].mask)
+        torch.testing.assert_close(regrouped.grad_weight, results[2].grad_weight,
+                                   rtol=1e-4, atol=1e-3)
         torch.cuda.synchronize()
         torch.save(
             {"begin": begin, "end": end,
