@@ -232,7 +232,7 @@ cudaError_t backward_of(const VariantArgs& a, cudaStream_t stream) {
         return error;
     }
     return launch_dependent(
-        rln_reduce_partials_kernel<8>, static_cast<unsigned>((2 * H + 31) / 32), 256u, stream,
+        rln_reduce_partials_kernel<32>, static_cast<unsigned>((2 * H + 31) / 32), 1024u, stream,
         static_cast<const float*>(a.partials), a.grad_parameters, grid, 2 * H);
 }
 

@@ -58,7 +58,7 @@ cudaError_t launch_reduce_partials(
     int partial_count,
     int columns,
     cudaStream_t stream) {
-    constexpr int kSegments = 8;
+    constexpr int kSegments = 32;  // one warp per range: 1,024 threads per 32 columns
     const int blocks = (columns + kWarpSize - 1) / kWarpSize;
     return launch_dependent(
         rln_reduce_partials_kernel<kSegments>,

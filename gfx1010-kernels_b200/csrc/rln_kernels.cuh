@@ -1113,6 +1113,11 @@ rln_backward_kernel(const BackwardParams p) {
 // Deterministic stage 2: out[c] = sum over CTA partials in a fixed order.
 // 32 columns x kSegments contiguous partial ranges per CTA; each range is
 // summed serially in index order, the ranges are combined in range order.
+// The partials were written a moment ago and sit in L2, so the kernel is bound
+// by load latency, not bandwidth: many short ranges (one warp each) and four
+// loads in flight per thread -- issued together, added in index order, so the
+// sum is the serial one -- keep the chains short (888 partials at H = 128:
+// 28 per range, 7 batches).
 // ---------------------------------------------------------------------------
 template <int kSegments>
 __global__ void __launch_bounds__(kSegments * kWarpSize)
@@ -1131,8 +1136,22 @@ rln_reduce_partials_kernel(
     const int end = min(partial_count, begin + per_segment);
     float sum = 0.0f;
     if (column < columns) {
-        for (int index = begin; index < end; ++index) {
-            sum += partials[static_cast<int64_t>(index) * columns + column];
+        const float* cursor = partials + static_cast<int64_t>(begin) * columns + column;
+        int index = begin;
+        for (; index + 4 <= end; index += 4) {
+            const float a = cursor[0];
+            const float b = cursor[columns];
+            const float c = cursor[2 * static_cast<int64_t>(columns)];
+            const float d = cursor[3 * static_cast<int64_t>(columns)];
+            sum += a;
+            sum += b;
+            sum += c;
+            sum += d;
+            cursor += 4 * static_cast<int64_t>(columns);
+        }
+        for (; index < end; ++index) {
+            sum += cursor[0];
+            cursor += columns;
         }
     }
     staged[segment][lane] = sum;
