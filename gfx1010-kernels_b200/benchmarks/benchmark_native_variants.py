@@ -93,6 +93,13 @@ VARIANTS = {
     "bwd_w4_c4": {"VARIANT_BWD_WARPS": 4, "VARIANT_BWD_CTAS_PER_SM": 4},
     "bwd_w8_c2": {"VARIANT_BWD_WARPS": 8, "VARIANT_BWD_CTAS_PER_SM": 2},
     "bwd_w6_c1": {"VARIANT_BWD_WARPS": 6, "VARIANT_BWD_CTAS_PER_SM": 1},
+    "bwd_w4_c5": {"VARIANT_BWD_WARPS": 4, "VARIANT_BWD_CTAS_PER_SM": 5},
+    "bwd_w4_c6": {"VARIANT_BWD_WARPS": 4, "VARIANT_BWD_CTAS_PER_SM": 6},
+    "bwd_w2_c8": {"VARIANT_BWD_WARPS": 2, "VARIANT_BWD_CTAS_PER_SM": 8},
+    "bwd_w2_c10": {"VARIANT_BWD_WARPS": 2, "VARIANT_BWD_CTAS_PER_SM": 10},
+    "bwd_w4_c2_r2": {"VARIANT_BWD_WARPS": 4, "VARIANT_BWD_CTAS_PER_SM": 2, "VARIANT_BWD_ROWS": 2},
+    "bwd_w4_c3_r2": {"VARIANT_BWD_WARPS": 4, "VARIANT_BWD_CTAS_PER_SM": 3, "VARIANT_BWD_ROWS": 2},
+    "bwd_w2_c4_r2": {"VARIANT_BWD_WARPS": 2, "VARIANT_BWD_CTAS_PER_SM": 4, "VARIANT_BWD_ROWS": 2},
 }
 DEFAULT_SET = ("shipped", "scalar_math", "packed_math", "mask_redux", "packed_redux",
                "bwd_static", "bwd_dynamic_all", "bwd_dynamic_tail3")
