@@ -69,6 +69,8 @@ VARIANTS = {
                          "VARIANT_FWD_WARPS": 1, "VARIANT_FWD_MIN_CTAS": 16},
     "packed_redux_c20": {"VARIANT_PACKED_FWD": 1, "VARIANT_PACKED_BWD": 1, "RLN_FWD_MASK_REDUX": 1,
                          "VARIANT_FWD_WARPS": 1, "VARIANT_FWD_MIN_CTAS": 20},
+    # the forward's first CTA clears the [2, H] buffer; no zeroing kernel in the step
+    "zero_in_forward": {"VARIANT_ZERO_IN_FORWARD": 1},
     # cache policy
     "stream_hints": {"VARIANT_STREAM_HINTS": 1},
     # forward geometry (wide rows): warps per CTA x resident CTAs per SM

@@ -14,6 +14,8 @@
 //   VARIANT_BWD_WARPS, VARIANT_BWD_ROWS, VARIANT_BWD_CTAS_PER_SM
 //   VARIANT_BWD_DYNAMIC    N > 0: the last N rounds of the backward's rows are claimed
 //                          through a counter (a huge N = every row but a warp's first)
+//   VARIANT_ZERO_IN_FORWARD  1: the forward's first CTA clears the [2, H] gradient buffer and
+//                          the step launches no zeroing kernel (step mode only is meaningful)
 //   VARIANT_HIDDEN         instantiate this width only (faster builds)
 //
 // fp16 branch, float32 normalized, dropout on, parameter gradients on, 16-byte
@@ -30,6 +32,9 @@
 #endif
 #ifndef VARIANT_BWD_DYNAMIC
 #define VARIANT_BWD_DYNAMIC 0
+#endif
+#ifndef VARIANT_ZERO_IN_FORWARD
+#define VARIANT_ZERO_IN_FORWARD 0
 #endif
 
 #if defined(__GNUC__)
@@ -133,8 +138,12 @@ ForwardParams forward_params(const VariantArgs& a) {
     p.threshold = static_cast<uint32_t>(static_cast<double>(a.dropout_p) * 4294967296.0);
     p.seed_lo = static_cast<uint32_t>(a.seed);
     p.seed_hi = static_cast<uint32_t>(a.seed >> 32);
-    p.offset_lo = static_cast<uint32_t>(a.offset);
-    p.offset_hi = static_cast<uint32_t>(a.offset >> 32);
+    p.offset_lo = static_cast<uint32_t>(a.offset >> 2);   // Philox block index = word offset / 4
+    p.offset_hi = static_cast<uint32_t>(a.offset >> 34);
+#if VARIANT_ZERO_IN_FORWARD
+    p.zero_buffer = reinterpret_cast<float4*>(a.grad_parameters);
+    p.zero_count4 = 2 * a.hidden / 4;
+#endif
     return p;
 }
 
@@ -191,7 +200,7 @@ cudaError_t forward_of(const VariantArgs& a, cudaStream_t stream) {
 
 // zeroing kernel + backward (+ fixed-order reduction in deterministic mode)
 template <int H>
-cudaError_t backward_of(const VariantArgs& a, cudaStream_t stream) {
+cudaError_t backward_of(const VariantArgs& a, cudaStream_t stream, bool fused_step) {
     using G = Geometry<H>;
     const int grid = backward_grid_of<H>(a);
     constexpr bool kDynamic = VARIANT_BWD_DYNAMIC != 0;
@@ -206,7 +215,7 @@ cudaError_t backward_of(const VariantArgs& a, cudaStream_t stream) {
         p.dynamic_begin = static_rounds * stride;
     }
     cudaError_t error = cudaSuccess;
-    if (!a.deterministic) {
+    if (!a.deterministic && !(VARIANT_ZERO_IN_FORWARD && fused_step)) {
         error = launch_dependent(
             rln_zero_kernel<256>, 1u + (2 * H / 4 - 1) / 256, 256u, stream,
             reinterpret_cast<float4*>(a.grad_parameters), 2 * H / 4,
@@ -275,7 +284,7 @@ VARIANT_API int rln_variant_run(const VariantArgs* args, int mode, int steps, vo
                 }
             }
             if (mode == 1 || mode == 2) {
-                const cudaError_t error = backward_of<H>(a, stream);
+                const cudaError_t error = backward_of<H>(a, stream, mode == 2);
                 if (error != cudaSuccess) {
                     return static_cast<int>(error);
                 }

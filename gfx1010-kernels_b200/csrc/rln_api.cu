@@ -190,6 +190,8 @@ int forward_launch(
     params.device_seed = device_seed;
     params.device_offset = device_offset;
     params.device_offset_extra = device_seed != nullptr ? offset : 0;
+    params.zero_buffer = nullptr;
+    params.zero_count4 = 0;
     if ((device_seed != nullptr || normalized_dtype != RLN_DTYPE_FLOAT32) && !vector_ok) {
         // the device-state kernels and the narrow-`normalized` kernels exist in
         // the vectorised form only

@@ -61,7 +61,25 @@ struct ForwardParams {
     const int64_t* device_seed;
     const int64_t* device_offset;
     uint64_t device_offset_extra;
+    // Optional (set by the variant benchmark only; the library passes NULL): a
+    // small buffer (16-byte aligned, zero_count4 float4 words) that the first
+    // CTA clears -- the [2, H] target of the following backward's atomics, so
+    // that no zeroing kernel stands between forward and backward.  Measured
+    // gain: about 1 us per step (the zeroing kernel is already hidden by
+    // programmatic dependent launch), too little to carry a buffer that the
+    // backward allocates today through the forward's interface.
+    float4* zero_buffer;
+    int zero_count4;
 };
+
+// The forward kernels' side job (see ForwardParams::zero_buffer).
+__device__ __forceinline__ void clear_side_buffer(const ForwardParams& p) {
+    if (p.zero_buffer != nullptr && blockIdx.x == 0) {
+        for (int i = threadIdx.x; i < p.zero_count4; i += blockDim.x) {
+            p.zero_buffer[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    }
+}
 
 struct PhiloxState {
     uint32_t seed_lo;
@@ -566,6 +584,7 @@ rln_forward_kernel(const ForwardParams p) {
     const int warp = threadIdx.x / kWarpSize;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRows;
     grid_dependency_sync();
+    clear_side_buffer(p);
     // Device state (graph capture): two loads, four registers.  Immediate
     // state: the four words are used straight from the kernel parameters
     // (constant-bank operands), see the Philox call below.
@@ -710,6 +729,7 @@ rln_forward_subwarp_kernel(const ForwardParams p) {
     const int row_in_warp = lane / kLanes;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarps * kRowsPerWarp;
     grid_dependency_sync();
+    clear_side_buffer(p);
     // Device state (graph capture): two loads, four registers.  Immediate
     // state: the four words are used straight from the kernel parameters
     // (constant-bank operands), see the Philox call below.
