@@ -49,6 +49,28 @@ class ResidualLayerNorm(nn.LayerNorm):
         # a half-precision activation without a separate cast kernel
         self.normalized_dtype = normalized_dtype
 
+    @classmethod
+    def from_layer_norm(cls, layer_norm, dropout_p=0.0, implementation="auto",
+                        normalized_dtype=None):
+        """Wrap an existing ``nn.LayerNorm`` of a model: the new module SHARES its
+        ``weight`` and ``bias`` parameters (same tensors, so the optimiser state,
+        the checkpoint keys of the original module and tied references stay
+        valid) and takes over its ``eps``.  The layer must normalise over the
+        last dimension only and have an affine weight and bias."""
+        if not isinstance(layer_norm, nn.LayerNorm):
+            raise TypeError("from_layer_norm expects an nn.LayerNorm")
+        if len(layer_norm.normalized_shape) != 1:
+            raise ValueError("ResidualLayerNorm normalises over the last dimension only")
+        if layer_norm.weight is None or layer_norm.bias is None:
+            raise ValueError("the LayerNorm must have an affine weight and bias")
+        module = cls(layer_norm.normalized_shape[0], dropout_p=dropout_p, eps=layer_norm.eps,
+                     implementation=implementation, device=layer_norm.weight.device,
+                     dtype=layer_norm.weight.dtype, normalized_dtype=normalized_dtype)
+        module.weight = layer_norm.weight
+        module.bias = layer_norm.bias
+        module.train(layer_norm.training)
+        return module
+
     @property
     def native_width(self):
         return self.normalized_shape[0] in NATIVE_HIDDEN_SIZES

@@ -75,3 +75,29 @@ def test_module_passes_normalized_dtype_through():
     assert updated.dtype == torch.float32 and normalized.dtype == torch.bfloat16
     assert "normalized_dtype=torch.bfloat16" in repr(module)
     assert "normalized_dtype" not in repr(ResidualLayerNorm(128))
+
+
+def test_from_layer_norm_shares_the_parameters_of_the_wrapped_module():
+    torch.manual_seed(0)
+    original = torch.nn.LayerNorm(128, eps=3e-5)
+    with torch.no_grad():
+        original.weight.normal_()
+        original.bias.normal_()
+    original.eval()
+    wrapped = ResidualLayerNorm.from_layer_norm(original, dropout_p=0.25, implementation="torch")
+    assert wrapped.weight is original.weight and wrapped.bias is original.bias
+    assert wrapped.eps == original.eps and wrapped.dropout_p == 0.25 and not wrapped.training
+    x, branch = torch.randn(5, 128), torch.randn(5, 128)
+    updated, normalized = wrapped(x, branch)
+    torch.testing.assert_close(updated, x + branch)
+    torch.testing.assert_close(normalized, original(x + branch))
+    # gradients land in the original module's parameters
+    wrapped.train()
+    wrapped(x, branch)[1].sum().backward()
+    assert original.weight.grad is not None and original.bias.grad is not None
+    with pytest.raises(ValueError):
+        ResidualLayerNorm.from_layer_norm(torch.nn.LayerNorm((4, 128)))
+    with pytest.raises(ValueError):
+        ResidualLayerNorm.from_layer_norm(torch.nn.LayerNorm(128, elementwise_affine=False))
+    with pytest.raises(TypeError):
+        ResidualLayerNorm.from_layer_norm(torch.nn.Linear(4, 4))
