@@ -230,7 +230,8 @@ class HostPipeline:
                  else _load().rln_sm100_host_forward_backward_enqueue)
         if not wait:
             # keep every tensor of the step alive until a wait has covered it
-            self._in_flight.append((tensors, out))
+            # (the step's number is filled in once the enqueue has succeeded)
+            self._in_flight.append([None, tensors, out])
         with torch.cuda.device(self.device):
             status = entry(
                 self._handle,
@@ -244,6 +245,8 @@ class HostPipeline:
         if status != 0 or wait:
             # (a failed enqueue has already waited for its copies in flight)
             self._in_flight.clear()
+        else:
+            self._in_flight[-1][0] = self.steps_enqueued()
         _check(status, "rln_sm100_host_forward_backward")
         return out
 
@@ -267,4 +270,8 @@ class HostPipeline:
                 self._in_flight.clear()
             else:
                 status = _load().rln_sm100_host_pipeline_wait_step(self._handle, int(step))
+                if status == 0:
+                    # steps land in order: everything up to `step` may be released
+                    self._in_flight = [entry for entry in self._in_flight
+                                       if entry[0] is None or entry[0] > int(step)]
         _check(status, "rln_sm100_host_pipeline_wait")
